@@ -19,9 +19,12 @@
 // 1 + coef * ln(floor((p + 1) / every) + 1); and values that ARE the keys (vd == 0 in the record: a page-layer
 // record then holds the keys alone and the read-out has the keys' size).  kv_write puts a step's keys and values,
 // as the product left them, into their pages; in a decode step the attention kernel does that itself (new_k_off).
+// A sink per head: exp(sink) joins the softmax's denominator, with no key and no value; and, with values that are
+// the keys, a read-out of only the first `od` elements of a key (a cache of latents with a positional tail: the
+// tail enters the scores alone).
 #include "common.cuh"
 
-#define MAX_HD 256
+#define MAX_HD 1024
 
 // A block per (row, head); its `nw` warps take the row's key tiles by turns (warp w: tiles w, w + nw, ...) and their
 // partial results are added in the order of the warps.  nw is the caller's constant for a layer (from its window), never
@@ -46,7 +49,8 @@ paged_attention_simt_kernel(const TA* __restrict__ q, const TC* __restrict__ poo
                             TA* __restrict__ out, int T, int H, int G, int hd, int page_tokens, int layer,
                             int layers_in_group, float scale, int window, int vd, int ldq, float softcap, int chunk,
                             const float* __restrict__ gate, int ldg, const float* __restrict__ slopes,
-                            float qt_coef, int qt_every, int new_k_off, int new_v_off, int* __restrict__ status) {
+                            float qt_coef, int qt_every, int new_k_off, int new_v_off, int* __restrict__ status,
+                            const float* __restrict__ sinks, int od) {
   FELLM_TRACE_SCOPE(TRACE_ATTENTION_SIMT);
   // new_k_off >= 0: a decode step, every row its request's only row.  The row's own key (and value) is read from the
   // row itself, at columns new_k_off (new_v_off) of q's rows, and written into its page here by the first head of
@@ -64,6 +68,7 @@ paged_attention_simt_kernel(const TA* __restrict__ q, const TC* __restrict__ poo
   const float slope = slopes ? slopes[h] : 0.f;
   const bool v_is_k = vd == 0;          // the values are the keys: nothing else is stored
   if (v_is_k) vd = hd;
+  const int ov = (v_is_k && od > 0) ? od : vd;       // elements of a value that are read out (values that are keys: the first od)
   float* parts = qs + ((hd + 7) & ~7);
   const int* bt = block_table + (size_t)row_slot[row] * max_pages;
   int k_begin = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
@@ -120,7 +125,7 @@ paged_attention_simt_kernel(const TA* __restrict__ q, const TC* __restrict__ poo
 #pragma unroll
       for (int i = 0; i < NACC; ++i) {
         int e = lane + 32 * i;
-        if (e < vd) acc[i] = fmaf(pj, to_f(vj[e]), acc[i]);
+        if (e < ov) acc[i] = fmaf(pj, to_f(vj[e]), acc[i]);
       }
     }
   }
@@ -142,32 +147,40 @@ paged_attention_simt_kernel(const TA* __restrict__ q, const TC* __restrict__ poo
   }
   if (nw > 1) {
     // the warps' parts, added in the order of the warps (a warp without a tile holds m = -inf, l = 0)
-    float* mine = parts + (size_t)w * (vd + 2);
+    float* mine = parts + (size_t)w * (ov + 2);
 #pragma unroll
-    for (int i = 0; i < NACC; ++i) { int e = lane + 32 * i; if (e < vd) mine[e] = acc[i]; }
-    if (lane == 0) { mine[vd] = m; mine[vd + 1] = l; }
+    for (int i = 0; i < NACC; ++i) { int e = lane + 32 * i; if (e < ov) mine[e] = acc[i]; }
+    if (lane == 0) { mine[ov] = m; mine[ov + 1] = l; }
     __syncthreads();
     if (w != 0) return;
     float M = -INFINITY;
-    for (int u = 0; u < nw; ++u) M = fmaxf(M, parts[(size_t)u * (vd + 2) + vd]);
+    for (int u = 0; u < nw; ++u) M = fmaxf(M, parts[(size_t)u * (ov + 2) + ov]);
     l = 0.f;
 #pragma unroll
     for (int i = 0; i < NACC; ++i) acc[i] = 0.f;
     for (int u = 0; u < nw; ++u) {
-      const float* pu = parts + (size_t)u * (vd + 2);
-      const float f = expf(pu[vd] - M);
-      l = fmaf(pu[vd + 1], f, l);
+      const float* pu = parts + (size_t)u * (ov + 2);
+      const float f = expf(pu[ov] - M);
+      l = fmaf(pu[ov + 1], f, l);
 #pragma unroll
-      for (int i = 0; i < NACC; ++i) { int e = lane + 32 * i; if (e < vd) acc[i] = fmaf(pu[e], f, acc[i]); }
+      for (int i = 0; i < NACC; ++i) { int e = lane + 32 * i; if (e < ov) acc[i] = fmaf(pu[e], f, acc[i]); }
     }
+    m = M;
   }
-  TA* o = out + ((size_t)row * H + h) * vd;
+  if (sinks) {
+    // a sink: one more term exp(sink) in the softmax's denominator, with no key and no value
+    const float sk = sinks[h], M2 = fmaxf(m, sk), f = expf(m - M2);
+    l = fmaf(l, f, expf(sk - M2));
+#pragma unroll
+    for (int i = 0; i < NACC; ++i) acc[i] *= f;
+  }
+  TA* o = out + ((size_t)row * H + h) * ov;
   float inv_l = 1.0f / l;
   if (gate) inv_l *= 1.0f / (1.0f + expf(-gate[(size_t)row * ldg + h]));
 #pragma unroll
   for (int i = 0; i < NACC; ++i) {
     int e = lane + 32 * i;
-    if (e < vd) o[e] = from_f<TA>(acc[i] * inv_l);
+    if (e < ov) o[e] = from_f<TA>(acc[i] * inv_l);
   }
 }
 
@@ -223,13 +236,17 @@ FELLM_API int fellm_paged_attention_general(const void* q, int act_bf16, const v
                                             int page_tokens, int layer, int layers_in_group, float scale,
                                             int window, int vd, int ldq, float softcap, int chunk, const float* gate,
                                             int ldg, const float* slopes, float qt_coef, int qt_every, int warps,
-                                            int new_k_off, int new_v_off, int* status, cudaStream_t stream) {
+                                            int new_k_off, int new_v_off, int* status, const float* sinks, int od,
+                                            cudaStream_t stream) {
+  // sinks float32 [H] or null: exp(sinks[h]) joins head h's softmax denominator.  od: with values that are the keys
+  // (vd == 0), only the first od elements of a key are read out (0: all hd).
   if (T <= 0) return 0;
   if (hd < 1 || hd > MAX_HD || vd < 0 || vd > MAX_HD || warps < 1 || warps > 8) return FELLM_ERR_SIZE;
+  if (od < 0 || od > hd || (od && vd)) return FELLM_ERR_SIZE;
   if (G < 1 || H % G) return FELLM_ERR_SIZE;
   if (!q || !pool || !block_table || !positions || !row_slot || !out) return FELLM_ERR_ARG;
   if (act_bf16 != cache_bf16) return FELLM_ERR_ARG;
-  const int out_d = vd ? vd : hd;
+  const int out_d = vd ? vd : (od ? od : hd);
   const size_t smem = ((size_t)((hd + 7) & ~7) + (size_t)warps * (out_d + 2)) * sizeof(float);
   const unsigned blocks = (unsigned)((long long)T * H);
   // 16 bytes of a key at a time where every key row starts on such a boundary
@@ -237,9 +254,10 @@ FELLM_API int fellm_paged_attention_general(const void* q, int act_bf16, const v
 #define PA(TA_, VEC_, NACC_) paged_attention_simt_kernel<TA_, TA_, VEC_, NACC_><<<blocks, warps * 32, smem, stream>>>((const TA_*)q, \
         (const TA_*)pool, block_table, max_pages, positions, row_slot, (TA_*)out, T, H, G, hd, page_tokens, \
         layer, layers_in_group, scale, window, vd, ldq, softcap, chunk, gate, ldg, slopes, qt_coef, qt_every, \
-        new_k_off, new_v_off, status)
+        new_k_off, new_v_off, status, sinks, od)
 #define PA_N(TA_, VEC_) do { if (out_d <= 32) PA(TA_, VEC_, 1); else if (out_d <= 64) PA(TA_, VEC_, 2); \
-                             else if (out_d <= 128) PA(TA_, VEC_, 4); else PA(TA_, VEC_, 8); } while (0)
+                             else if (out_d <= 128) PA(TA_, VEC_, 4); else if (out_d <= 256) PA(TA_, VEC_, 8); \
+                             else if (out_d <= 512) PA(TA_, VEC_, 16); else PA(TA_, VEC_, 32); } while (0)
   if (act_bf16) { if (vec) PA_N(bf16, true); else PA_N(bf16, false); }
   else { if (vec) PA_N(float, true); else PA_N(float, false); }
 #undef PA_N
@@ -254,5 +272,5 @@ FELLM_API int fellm_paged_attention_simt(const void* q, int act_bf16, const void
                                          int window, cudaStream_t stream) {
   return fellm_paged_attention_general(q, act_bf16, pool, cache_bf16, block_table, max_pages, positions, row_slot, out,
                                        T, H, G, hd, page_tokens, layer, layers_in_group, scale, window, hd, H * hd, 0.f,
-                                       0, nullptr, 0, nullptr, 0.f, 0, 1, -1, -1, nullptr, stream);
+                                       0, nullptr, 0, nullptr, 0.f, 0, 1, -1, -1, nullptr, nullptr, 0, stream);
 }

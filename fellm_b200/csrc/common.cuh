@@ -29,6 +29,17 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// Gate and up of a gated feed-forward -> its activation.  limit <= 0: SiLU(g) * u.  limit > 0: the clamped form,
+// g = min(g, limit), u = clamp(u, -limit, limit), g * sigmoid(alpha g) * (u + 1).
+__device__ __forceinline__ float glu_act(float g, float u, float limit, float alpha) {
+  if (limit > 0.f) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+  }
+  return g / (1.0f + expf(-g)) * u;
+}
+
 // ---- programmatic dependent launch: a kernel launched with launch_k() may start while its
 // predecessor in the stream is still running.  What does not depend on the predecessor (weight
 // prefetch, index set-up) goes before pdl_wait(); everything that reads or writes data another

@@ -255,3 +255,187 @@ FELLM_API int fellm_scale_softcap(float* z, long long n, float scale, float cap,
   scale_softcap_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(z, n, scale, cap);
   return launch_status();
 }
+
+// ---------------------------------------------------------------- a block's sum, the same order for every row
+// Sum of v over the block (blockDim.x a multiple of 32, at most 1024): lanes by a butterfly, warps in order.
+__device__ __forceinline__ float block_sum(float v, float* scratch /* [33] */) {
+  v = warp_sum(v);
+  __syncthreads();                          // the scratch may still be read from the call before
+  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int i = 0; i < (int)(blockDim.x >> 5); ++i) t += scratch[i];
+    scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
+// ---------------------------------------------------------------- RMSNorm in groups
+// The row in `groups` equal consecutive parts, each over its own root mean square, then the weight:
+// y[c] = x[c] / sqrt(mean over c's part of x^2 + eps) * w[c].  A block per (row, part); float32 in, activation dtype out.
+template <typename TO>
+__global__ void __launch_bounds__(256)
+rmsnorm_groups_kernel(const float* __restrict__ x, const float* __restrict__ w, TO* __restrict__ out,
+                      const int* __restrict__ rows, int d, int groups, float eps) {
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int orow = blockIdx.x, g = blockIdx.y, per = d / groups;
+  const int irow = rows ? rows[orow] : orow;
+  const float* xr = x + (size_t)irow * d + (size_t)g * per;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < per; i += blockDim.x) { float v = xr[i]; ss = fmaf(v, v, ss); }
+  const float scale = 1.0f / sqrtf(block_sum(ss, scratch) / (float)per + eps);
+  TO* o = out + (size_t)orow * d + (size_t)g * per;
+  const float* wg = w + (size_t)g * per;
+  for (int i = threadIdx.x; i < per; i += blockDim.x) o[i] = from_f<TO>((xr[i] * scale) * wg[i]);
+}
+
+FELLM_API int fellm_rmsnorm_groups(const float* x, const float* w, void* out, int out_is_bf16, const int* rows,
+                                   int n_out_rows, int d, int groups, float eps, cudaStream_t stream) {
+  if (n_out_rows <= 0) return 0;
+  if (!x || !w || !out) return FELLM_ERR_ARG;
+  if (groups < 1 || d % groups || groups > 65535) return FELLM_ERR_SIZE;
+  const int per = d / groups, threads = per >= 1024 ? 256 : (per >= 256 ? 128 : 64);
+  dim3 grid(n_out_rows, groups);
+  if (out_is_bf16) return launch_k_class(launch_class_for_rows(n_out_rows, 0), rmsnorm_groups_kernel<bf16>, grid, dim3(threads), 0, stream, 1, x, w, (bf16*)out, rows, d, groups, eps);
+  return launch_k_class(launch_class_for_rows(n_out_rows, 0), rmsnorm_groups_kernel<float>, grid, dim3(threads), 0, stream, 1, x, w, (float*)out, rows, d, groups, eps);
+}
+
+// ---------------------------------------------------------------- polynomial activation over unit powers
+// out = a N(z) + b N(z^2) + c N(z^3) + e, powers element by element, N(v) = v / sqrt(mean(v^2) + eps) over the row;
+// coef = (a, b, c, e) on the device.  z float32 [T, F] (the product's sums as they are), out in the activation dtype.
+template <typename TO>
+__global__ void __launch_bounds__(256)
+poly_norm_kernel(const float* __restrict__ z, const float* __restrict__ coef, TO* __restrict__ out, int F, float eps) {
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const float* zr = z + (size_t)blockIdx.x * F;
+  float s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  for (int i = threadIdx.x; i < F; i += blockDim.x) {
+    const float v = zr[i], v2 = v * v, v3 = v2 * v;
+    s1 = fmaf(v, v, s1); s2 = fmaf(v2, v2, s2); s3 = fmaf(v3, v3, s3);
+  }
+  const float r1 = coef[0] / sqrtf(block_sum(s1, scratch) / (float)F + eps);
+  const float r2 = coef[1] / sqrtf(block_sum(s2, scratch) / (float)F + eps);
+  const float r3 = coef[2] / sqrtf(block_sum(s3, scratch) / (float)F + eps);
+  const float e = coef[3];
+  TO* o = out + (size_t)blockIdx.x * F;
+  for (int i = threadIdx.x; i < F; i += blockDim.x) {
+    const float v = zr[i], v2 = v * v;
+    o[i] = from_f<TO>(fmaf(v, r1, fmaf(v2, r2, fmaf(v2 * v, r3, e))));
+  }
+}
+
+FELLM_API int fellm_poly_norm(const float* z, const float* coef, void* out, int out_is_bf16, int rows, int F, float eps,
+                              cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (!z || !coef || !out || F < 1) return FELLM_ERR_ARG;
+  const int threads = F >= 1024 ? 256 : 128;
+  if (out_is_bf16) return launch_k_class(launch_class_for_rows(rows, 0), poly_norm_kernel<bf16>, dim3(rows), dim3(threads), 0, stream, 1, z, coef, (bf16*)out, F, eps);
+  return launch_k_class(launch_class_for_rows(rows, 0), poly_norm_kernel<float>, dim3(rows), dim3(threads), 0, stream, 1, z, coef, (float*)out, F, eps);
+}
+
+// ---------------------------------------------------------------- sublayers through sigmoid gates into the stream
+// x[t, c] += sum over the n sublayers s of y_s[t, c] * sigmoid(zg[t, s * d + c])   (zg: the gates' logits, bias
+// included, float32 [T, ldg]; y_s float32 [T, d]; n = 1 or 2; the sublayers are added up first, in order)
+__global__ void gated_add_kernel(float* __restrict__ x, const float* __restrict__ y0, const float* __restrict__ y1,
+                                 const float* __restrict__ zg, int ldg, long long n, int d) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / d; const int c = (int)(i - t * d);
+    const float* g = zg + t * ldg;
+    float v = y0[i] / (1.0f + expf(-g[c]));
+    if (y1) v += y1[i] / (1.0f + expf(-g[d + c]));
+    x[i] += v;
+  }
+}
+
+FELLM_API int fellm_gated_add(float* x, const float* y0, const float* y1, const float* zg, int ldg, int rows, int d,
+                              cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (!x || !y0 || !zg || d < 1) return FELLM_ERR_ARG;
+  const long long n = (long long)rows * d;
+  long long blocks = (n + 255) / 256; if (blocks > fellm_sm_count() * 16) blocks = fellm_sm_count() * 16;
+  return launch_k_class(launch_class_for_rows(rows, 0), gated_add_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, 1, x, y0, y1, zg, ldg, n, d);
+}
+
+// ---------------------------------------------------------------- what a token adds to the stream by itself
+// e = table[token, off : off + m];  g = gelu_tanh(Wg x) * e;  y = Wp g;  x += y / sqrt(mean(y^2) + eps) * w
+// (Wg [m, d], Wp [d, m], w float32 [d]; x float32, updated in place).  A block per row, float32 sums: every dot
+// product over d is a lane's share in order and a butterfly, every sum over m runs in order.
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+  return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+template <typename TW>
+__global__ void __launch_bounds__(256)
+token_side_kernel(float* __restrict__ x, const int* __restrict__ tokens, const TW* __restrict__ table, int ldt, int off,
+                  int vocab, const TW* __restrict__ Wg, const TW* __restrict__ Wp, const float* __restrict__ w, int d, int m,
+                  float eps, int* __restrict__ status) {
+  extern __shared__ float sh[];            // [d] the row, then its y; [m] g
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  float* xs = sh; float* gs = sh + d;
+  float* xr = x + (size_t)blockIdx.x * d;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) xs[i] = xr[i];
+  int tok = tokens[blockIdx.x];
+  const bool bad = tok < 0 || tok >= vocab;
+  if (bad) { if (threadIdx.x == 0 && status) atomicExch(status, 1); tok = 0; }
+  __syncthreads();
+  for (int j = warp; j < m; j += nw) {
+    const TW* wr = Wg + (size_t)j * d;
+    float s = 0.f;
+    for (int k = lane; k < d; k += 32) s = fmaf(xs[k], to_f(wr[k]), s);
+    s = warp_sum(s);
+    if (lane == 0) gs[j] = bad ? 0.f : gelu_tanh_f(s) * to_f(table[(size_t)tok * ldt + off + j]);
+  }
+  __syncthreads();
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    const TW* pr = Wp + (size_t)i * m;
+    float y = 0.f;
+    for (int j = 0; j < m; ++j) y = fmaf(gs[j], to_f(pr[j]), y);
+    xs[i] = y;                              // (a thread overwrites only the elements it owns; the row was read before the barrier)
+    ss = fmaf(y, y, ss);
+  }
+  const float scale = 1.0f / sqrtf(block_sum(ss, scratch) / (float)d + eps);
+  for (int i = threadIdx.x; i < d; i += blockDim.x) xr[i] += (xs[i] * scale) * w[i];
+}
+
+FELLM_API int fellm_token_side(float* x, const int* tokens, const void* table, int ldt, int off, int vocab, const void* Wg,
+                               const void* Wp, int w_bf16, const float* w, int rows, int d, int m, float eps, int* status,
+                               cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (!x || !tokens || !table || !Wg || !Wp || !w) return FELLM_ERR_ARG;
+  const size_t smem = (size_t)(d + m) * sizeof(float);
+  if (d < 1 || m < 1 || smem > 200 * 1024) return FELLM_ERR_SIZE;
+  const int cls = launch_class_for_rows(rows, 0);
+  if (w_bf16) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(token_side_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return launch_k_class(cls, token_side_kernel<bf16>, dim3(rows), dim3(256), smem, stream, 1, x, tokens, (const bf16*)table, ldt, off, vocab,
+                          (const bf16*)Wg, (const bf16*)Wp, w, d, m, eps, status);
+  }
+  if (smem > 48 * 1024) cudaFuncSetAttribute(token_side_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  return launch_k_class(cls, token_side_kernel<float>, dim3(rows), dim3(256), smem, stream, 1, x, tokens, (const float*)table, ldt, off, vocab,
+                        (const float*)Wg, (const float*)Wp, w, d, m, eps, status);
+}
+
+// ---------------------------------------------------------------- one stream added to another
+// x += y   (float32; the embedding's output added again where a pass of a looped run of layers opens)
+__global__ void add_rows_kernel(float* __restrict__ x, const float* __restrict__ y, long long n) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) x[i] += y[i];
+}
+
+FELLM_API int fellm_add_rows(float* x, const float* y, long long n, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (!x || !y) return FELLM_ERR_ARG;
+  long long blocks = (n + 255) / 256; if (blocks > fellm_sm_count() * 16) blocks = fellm_sm_count() * 16;
+  add_rows_kernel<<<(unsigned)blocks, 256, 0, stream>>>(x, y, n);
+  return launch_status();
+}

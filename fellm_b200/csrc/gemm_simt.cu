@@ -16,8 +16,11 @@
 template <typename TA, typename TW, typename TO, int EPI>
 __global__ void __launch_bounds__(256)
 gemm_tn_simt_kernel(const TA* __restrict__ A, const TW* __restrict__ W, const float* __restrict__ bias,
-                    TO* __restrict__ C, int M, int N, int K, int lda, int ldw, int ldc) {
+                    TO* __restrict__ C, int M, int N, int K, int lda, int ldw, int ldc,
+                    long long sa = 0, long long sw = 0, long long sc = 0) {
   FELLM_TRACE_SCOPE(TRACE_GEMM_SIMT);
+  // a batch of products (blockIdx.z): member b reads A + b sa, W + b sw and writes C + b sc (elements)
+  A += (size_t)blockIdx.z * sa; W += (size_t)blockIdx.z * sw; C += (size_t)blockIdx.z * sc;
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   int tid = threadIdx.x;
@@ -99,4 +102,28 @@ FELLM_API int fellm_gemm_simt(const void* A, int a_dt, const void* W, int w_dt, 
     case 7: return launch_epi<bf16, bf16, bf16>(A, W, bias, C, M, N, K, lda, ldw, ldc, accumulate, s);
     default: return FELLM_ERR_ARG;   // float32 activations never round down to a bfloat16 result
   }
+}
+
+// A batch of such products in one launch: member b computes C_b[M, N] = A_b[M, K] W_b[N, K]^T with A_b = A + b sa,
+// W_b = W + b sw, C_b = C + b sc (strides in elements): the heads of a layer, each with a matrix of its own, on
+// column blocks of the same rows.  Every output is the same k-ordered chain as in the single product.
+FELLM_API int fellm_gemm_simt_batched(const void* A, int a_dt, const void* W, int w_dt, void* C, int c_dt, int batch,
+                                      int M, int N, int K, int lda, int ldw, int ldc, long long sa, long long sw,
+                                      long long sc, cudaStream_t s) {
+  if (M <= 0 || N <= 0 || batch <= 0) return 0;
+  if (!A || !W || !C || K <= 0) return FELLM_ERR_ARG;
+  if (batch > 65535) return FELLM_ERR_SIZE;
+  dim3 grid(ceil_div(N, BN), ceil_div(M, BM), batch);
+#define BATCHED(TA_, TW_, TO_) gemm_tn_simt_kernel<TA_, TW_, TO_, 0><<<grid, 256, 0, s>>>((const TA_*)A, (const TW_*)W, nullptr, (TO_*)C, M, N, K, lda, ldw, ldc, sa, sw, sc)
+  switch (a_dt * 4 + w_dt * 2 + c_dt) {
+    case 0: BATCHED(float, float, float); break;
+    case 2: BATCHED(float, bf16, float); break;
+    case 4: BATCHED(bf16, float, float); break;
+    case 5: BATCHED(bf16, float, bf16); break;
+    case 6: BATCHED(bf16, bf16, float); break;
+    case 7: BATCHED(bf16, bf16, bf16); break;
+    default: return FELLM_ERR_ARG;
+  }
+#undef BATCHED
+  return launch_status();
 }

@@ -103,6 +103,7 @@ struct UmmaArgs {
   // grouped form (gemm_umma_kernel<.., true>): row tile r of A is rows g_table[3r + 1] .. + g_table[3r + 2] and is
   // multiplied by the matrix of group g_table[3r], whose rows start at g_table[3r] * g_wrows of W; *g_tiles row tiles
   const int* g_table; const int* g_tiles; int g_wrows;
+  float glu_limit = 0.f, glu_alpha = 1.f;     // the gated epilogue's activation (glu_act): 0 = SiLU(gate) * up
 };
 
 // One 32-column chunk of an output row: v[j] is C[m][n + j].
@@ -120,7 +121,7 @@ __device__ __forceinline__ void store_chunk(const UmmaArgs& a, float* v, int m, 
       for (int j = 0; j < 8; j += 2) {
         float g0 = v[16 * h + j], g1 = v[16 * h + j + 1], u0 = v[16 * h + 8 + j], u1 = v[16 * h + 9 + j];
         if (a.bias) { g0 += a.bias[n + 16 * h + j]; g1 += a.bias[n + 16 * h + j + 1]; u0 += a.bias[n + 16 * h + 8 + j]; u1 += a.bias[n + 16 * h + 9 + j]; }
-        __nv_bfloat162 p = __floats2bfloat162_rn((g0 / (1.0f + expf(-g0))) * u0, (g1 / (1.0f + expf(-g1))) * u1);
+        __nv_bfloat162 p = __floats2bfloat162_rn(glu_act(g0, u0, a.glu_limit, a.glu_alpha), glu_act(g1, u1, a.glu_limit, a.glu_alpha));
         packed[j >> 1] = *(unsigned*)&p;
       }
       *(uint4*)(dst + 8 * h) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
@@ -788,7 +789,7 @@ FELLM_API int fellm_gemm_umma(const void* A, const void* W, const float* bias, v
 // behind its own too (the next group's, or zeros past P); their sums are computed and never stored.
 FELLM_API int fellm_gemm_umma_grouped(const void* A, const void* W, void* out, int epi, int P, int N, int K, int groups,
                                       int lda, int ldo, const int* table, const int* n_tiles, int max_tiles, int* status,
-                                      cudaStream_t stream) {
+                                      float glu_limit, float glu_alpha, cudaStream_t stream) {
   if (P <= 0 || N <= 0 || max_tiles <= 0) return 0;
   if (!A || !W || !out || !table || !n_tiles || K <= 0 || groups < 1) return FELLM_ERR_ARG;
   if ((K % 8) || (lda % 8) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return FELLM_ERR_SIZE;
@@ -802,6 +803,7 @@ FELLM_API int fellm_gemm_umma_grouped(const void* A, const void* W, void* out, i
   if (e) return e;
   UmmaArgs a; a.bias = nullptr; a.out = out; a.status = status; a.M = P; a.N = N; a.K = K; a.ldo = ldo;
   a.g_table = table; a.g_tiles = n_tiles; a.g_wrows = N;
+  a.glu_limit = glu_limit; a.glu_alpha = glu_alpha;
   if (epi == EPI_SWIGLU) return wide ? launch_grouped<EPI_SWIGLU, 256>(ma, mw, a, max_tiles, stream) : launch_grouped<EPI_SWIGLU, 128>(ma, mw, a, max_tiles, stream);
   return wide ? launch_grouped<EPI_F32, 256>(ma, mw, a, max_tiles, stream) : launch_grouped<EPI_F32, 128>(ma, mw, a, max_tiles, stream);
 }

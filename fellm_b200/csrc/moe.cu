@@ -61,6 +61,86 @@ __device__ __forceinline__ void route_warp(const float* z, int E, int top, int r
   }
 }
 
+// One warp, the sigmoid form: scores s_e = sigmoid(z_e); the choice looks at s_e + corr_e (corr may be null) and only
+// inside the `keep` groups (of n_groups equal groups of neighbouring experts) whose `gtop` largest choice scores sum
+// highest (ties: the lower group); the `top` largest choice scores among those (ties: the lower expert); weights = the
+// chosen experts' plain scores, over their sum + 1e-20 when renorm.  work: shared memory of E + n_groups floats.
+__device__ __forceinline__ void route_sigmoid_warp(const float* z, const float* corr, int E, int top, int renorm,
+                                                   int n_groups, int keep, int gtop, float* work, int* idx, float* w, int lane) {
+  float* choice = work;                 // [E]
+  float* gscore = work + E;             // [n_groups]; -inf once a group is taken, then +inf marks the kept ones
+  for (int e = lane; e < E; e += 32) choice[e] = 1.0f / (1.0f + expf(-z[e])) + (corr ? corr[e] : 0.f);
+  __syncwarp();
+  if (n_groups > 1 && keep < n_groups) {
+    const int per = E / n_groups;
+    for (int g = lane; g < n_groups; g += 32) {
+      // the sum of the group's gtop largest choice scores: gtop passes over the group, each taking the next largest
+      float sum = 0.f;
+      int last_i = -1; float last_v = INFINITY;
+      for (int c = 0; c < gtop && c < per; ++c) {
+        float best = -INFINITY; int bi = -1;
+        for (int i = 0; i < per; ++i) {
+          const float v = choice[g * per + i];
+          const bool after = v < last_v || (v == last_v && i > last_i);      // not yet taken, in (value desc, index asc) order
+          if (after && (bi < 0 || v > best)) { best = v; bi = i; }
+        }
+        sum += best; last_v = best; last_i = bi;
+      }
+      gscore[g] = sum;
+    }
+    __syncwarp();
+    for (int c = 0; c < keep; ++c) {
+      float best = -INFINITY; int bi = 0x7fffffff;
+      for (int g = lane; g < n_groups; g += 32) {
+        const float v = gscore[g];
+        if (v != INFINITY && (bi == 0x7fffffff || v > best || (v == best && g < bi))) { best = v; bi = g; }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > best || (ov == best && oi < bi))) { best = ov; bi = oi; }
+      }
+      if (lane == 0 && bi != 0x7fffffff) gscore[bi] = INFINITY;
+      __syncwarp();
+    }
+    for (int e = lane; e < E; e += 32) if (gscore[e / per] != INFINITY) choice[e] = -INFINITY;
+    __syncwarp();
+  }
+  int taken[MOE_MAX_TOP];
+  float tw[MOE_MAX_TOP];
+  float chosen = 0.f;
+#pragma unroll
+  for (int c = 0; c < MOE_MAX_TOP; ++c) {
+    if (c >= top) break;
+    float best = -INFINITY; int bi = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      bool free_ = true;
+#pragma unroll
+      for (int p = 0; p < MOE_MAX_TOP; ++p) if (p < c && taken[p] == e) free_ = false;
+      const float v = choice[e];
+      if (free_ && (bi == 0x7fffffff || v > best || (v == best && e < bi))) { best = v; bi = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > best || (ov == best && oi < bi))) { best = ov; bi = oi; }
+    }
+    taken[c] = bi;
+    tw[c] = 1.0f / (1.0f + expf(-z[bi]));
+    chosen += tw[c];
+  }
+  if (lane == 0) {
+#pragma unroll
+    for (int c = 0; c < MOE_MAX_TOP; ++c) {
+      if (c >= top) break;
+      idx[c] = taken[c];
+      w[c] = renorm ? tw[c] / (chosen + 1e-20f) : tw[c];
+    }
+  }
+}
+
 // One warp per token.  logits float32 [T, ld]; idx [T, top] int32; w [T, top] float32.
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const float* __restrict__ logits, int ld, int T, int E, int top, int renorm,
@@ -86,8 +166,9 @@ FELLM_API int fellm_moe_route(const float* logits, int ld, int T, int E, int top
 template <typename TA, typename TW>
 __global__ void __launch_bounds__(ROUTER_WARPS * 32)
 moe_router_kernel(const TA* __restrict__ h, int ldh, const TW* __restrict__ Wr, int K, int E, int top, int renorm,
-                  int* __restrict__ idx, float* __restrict__ w) {
-  extern __shared__ float zs[];                 // [E]
+                  int* __restrict__ idx, float* __restrict__ w, int sigmoid, const float* __restrict__ corr,
+                  int n_groups, int keep, int gtop) {
+  extern __shared__ float zs[];                 // [E]; the sigmoid form: + [E + n_groups]
   const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const TA* hr = h + (size_t)t * ldh;
   for (int e = warp; e < E; e += ROUTER_WARPS) {
@@ -98,16 +179,24 @@ moe_router_kernel(const TA* __restrict__ h, int ldh, const TW* __restrict__ Wr, 
     if (lane == 0) zs[e] = s;
   }
   __syncthreads();
-  if (warp == 0) route_warp(zs, E, top, renorm, idx + (size_t)t * top, w + (size_t)t * top, lane);
+  if (warp == 0) {
+    if (sigmoid) route_sigmoid_warp(zs, corr, E, top, renorm, n_groups, keep, gtop, zs + E, idx + (size_t)t * top, w + (size_t)t * top, lane);
+    else route_warp(zs, E, top, renorm, idx + (size_t)t * top, w + (size_t)t * top, lane);
+  }
 }
 
 FELLM_API int fellm_moe_router(const void* h, int h_bf16, int ldh, const void* Wr, int w_bf16, int T, int K, int E, int top,
-                               int renorm, int* idx, float* w, cudaStream_t stream) {
+                               int renorm, int* idx, float* w, int sigmoid, const float* corr, int n_groups, int keep,
+                               int gtop, cudaStream_t stream) {
+  // sigmoid = 0: softmax scores over all experts.  sigmoid = 1: sigmoid scores, a correction added for the choice
+  // (corr float32 [E] or null), the choice limited to `keep` of n_groups groups ranked by their gtop best choice scores.
   if (T <= 0) return 0;
-  if (E < 1 || top < 1 || top > E || top > MOE_MAX_TOP || (size_t)E * sizeof(float) > 48 * 1024) return FELLM_ERR_SIZE;
+  if (n_groups < 1) n_groups = 1;
+  if (E < 1 || top < 1 || top > E || top > MOE_MAX_TOP || (size_t)(2 * E + n_groups) * sizeof(float) > 48 * 1024) return FELLM_ERR_SIZE;
+  if (sigmoid && (E % n_groups || keep < 1 || keep > n_groups || gtop < 1 || top > (E / n_groups) * keep)) return FELLM_ERR_SIZE;
   if (!h || !Wr || !idx || !w) return FELLM_ERR_ARG;
-  const size_t sh = (size_t)E * sizeof(float);
-#define ROUTER(TA_, TW_) moe_router_kernel<TA_, TW_><<<T, ROUTER_WARPS * 32, sh, stream>>>((const TA_*)h, ldh, (const TW_*)Wr, K, E, top, renorm, idx, w)
+  const size_t sh = (size_t)(sigmoid ? 2 * E + n_groups : E) * sizeof(float);
+#define ROUTER(TA_, TW_) moe_router_kernel<TA_, TW_><<<T, ROUTER_WARPS * 32, sh, stream>>>((const TA_*)h, ldh, (const TW_*)Wr, K, E, top, renorm, idx, w, sigmoid, corr, n_groups, keep, gtop)
   if (h_bf16) { if (w_bf16) ROUTER(bf16, bf16); else ROUTER(bf16, float); }
   else { if (w_bf16) ROUTER(float, bf16); else ROUTER(float, float); }
 #undef ROUTER
@@ -247,7 +336,7 @@ template <typename TA, typename TW, typename TO, bool GATED>
 __global__ void __launch_bounds__(256)
 moe_gemm_fma_kernel(const TA* __restrict__ A, int lda, const int* __restrict__ gather, int top,
                     const TW* __restrict__ W, TO* __restrict__ C, int ldc, int N, int K,
-                    const int* __restrict__ table, const int* __restrict__ n_tiles, int inter) {
+                    const int* __restrict__ table, const int* __restrict__ n_tiles, int inter, float act_limit, float act_alpha) {
   if ((int)blockIdx.x >= *n_tiles) return;
   __shared__ float As[FK][FB + 1];
   __shared__ float Ws[GATED ? 2 : 1][FK][FB + 1];
@@ -304,7 +393,7 @@ moe_gemm_fma_kernel(const TA* __restrict__ A, int lda, const int* __restrict__ g
       if (GATED) {
         // in the bfloat16 engine gate and up are activations like those of the dense feed-forward: rounded first
         float g = to_f(from_f<TA>(v)), u = to_f(from_f<TA>(acc2[i][j]));
-        v = g / (1.0f + expf(-g)) * u;
+        v = glu_act(g, u, act_limit, act_alpha);
       }
       C[(size_t)(row0 + r) * ldc + n] = from_f<TO>(v);
     }
@@ -328,7 +417,7 @@ template <typename TO, bool GATED>
 __global__ void __launch_bounds__(128)
 moe_gemm_mma_kernel(const bf16* __restrict__ A, int lda, const int* __restrict__ gather, int top,
                     const bf16* __restrict__ W, TO* __restrict__ C, int ldc, int N, int K,
-                    const int* __restrict__ table, const int* __restrict__ n_tiles, int inter) {
+                    const int* __restrict__ table, const int* __restrict__ n_tiles, int inter, float act_limit, float act_alpha) {
   if ((int)blockIdx.x >= *n_tiles) return;
   __shared__ __align__(16) bf16 As[2][TB * TLD];
   __shared__ __align__(16) bf16 Ws[2][(GATED ? 2 : 1) * TB * TLD];
@@ -400,7 +489,7 @@ moe_gemm_mma_kernel(const bf16* __restrict__ A, int lda, const int* __restrict__
         float v = acc[j][half * 2 + c];
         if (GATED) {
           const float g = to_f(from_f<bf16>(v)), u = to_f(from_f<bf16>(acc[8 + j][half * 2 + c]));
-          v = g / (1.0f + expf(-g)) * u;
+          v = glu_act(g, u, act_limit, act_alpha);
         }
         C[(size_t)(row0 + r) * ldc + n] = from_f<TO>(v);
       }
@@ -424,7 +513,7 @@ template <typename TO, bool GATED>
 __global__ void __launch_bounds__(VW * 32)
 moe_gemv_kernel(const bf16* __restrict__ A, int lda, const int* __restrict__ gather, int top,
                 const bf16* __restrict__ W, TO* __restrict__ C, int ldc, int N, int K,
-                const int* __restrict__ table, const int* __restrict__ n_tiles, int inter) {
+                const int* __restrict__ table, const int* __restrict__ n_tiles, int inter, float act_limit, float act_alpha) {
   if ((int)blockIdx.x >= *n_tiles) return;
   const int e = table[3 * blockIdx.x], row0 = table[3 * blockIdx.x + 1], rows = table[3 * blockIdx.x + 2];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -475,7 +564,7 @@ moe_gemv_kernel(const bf16* __restrict__ A, int lda, const int* __restrict__ gat
       if (lane == 0 && r0 + i < rows) {
         if (GATED) {
           a = to_f(from_f<bf16>(a)); b = to_f(from_f<bf16>(b));
-          C[(size_t)(row0 + r0 + i) * ldc + n] = from_f<TO>(a / (1.0f + expf(-a)) * b);
+          C[(size_t)(row0 + r0 + i) * ldc + n] = from_f<TO>(glu_act(a, b, act_limit, act_alpha));
         } else {
           C[(size_t)(row0 + r0 + i) * ldc + n] = from_f<TO>(a);
           if (two) C[(size_t)(row0 + r0 + i) * ldc + n + 1] = from_f<TO>(b);
@@ -489,7 +578,7 @@ moe_gemv_kernel(const bf16* __restrict__ A, int lda, const int* __restrict__ gat
 // when gated (the activation), float32 otherwise.  max_tiles: the table's capacity = the launch's first extent.
 FELLM_API int fellm_moe_gemm(const void* A, int a_bf16, int lda, const int* gather, int top, const void* W, int w_bf16,
                              void* C, int c_bf16, int ldc, int N, int K, int gated, const int* table, const int* n_tiles,
-                             int max_tiles, int use_mma, int inter, int few_rows, cudaStream_t stream) {
+                             int max_tiles, int use_mma, int inter, int few_rows, float act_limit, float act_alpha, cudaStream_t stream) {
   if (max_tiles <= 0) return 0;
   if (N < 1 || K < 1 || top < 1) return FELLM_ERR_SIZE;
   if (!A || !W || !C || !table || !n_tiles) return FELLM_ERR_ARG;
@@ -498,30 +587,30 @@ FELLM_API int fellm_moe_gemm(const void* A, int a_bf16, int lda, const int* gath
   if (mma && few_rows) {
     dim3 grid(max_tiles, gated ? (N + VW - 1) / VW : (N + 2 * VW - 1) / (2 * VW));
     if (gated)
-      moe_gemv_kernel<bf16, true><<<grid, VW * 32, 0, stream>>>((const bf16*)A, lda, gather, top, (const bf16*)W, (bf16*)C, ldc, N, K, table, n_tiles, inter);
+      moe_gemv_kernel<bf16, true><<<grid, VW * 32, 0, stream>>>((const bf16*)A, lda, gather, top, (const bf16*)W, (bf16*)C, ldc, N, K, table, n_tiles, inter, act_limit, act_alpha);
     else
-      moe_gemv_kernel<float, false><<<grid, VW * 32, 0, stream>>>((const bf16*)A, lda, gather, top, (const bf16*)W, (float*)C, ldc, N, K, table, n_tiles, inter);
+      moe_gemv_kernel<float, false><<<grid, VW * 32, 0, stream>>>((const bf16*)A, lda, gather, top, (const bf16*)W, (float*)C, ldc, N, K, table, n_tiles, inter, act_limit, act_alpha);
     return launch_status();
   }
   if (mma) {
     dim3 grid(max_tiles, (N + TB - 1) / TB);
     if (gated)
-      moe_gemm_mma_kernel<bf16, true><<<grid, 128, 0, stream>>>((const bf16*)A, lda, gather, top, (const bf16*)W, (bf16*)C, ldc, N, K, table, n_tiles, inter);
+      moe_gemm_mma_kernel<bf16, true><<<grid, 128, 0, stream>>>((const bf16*)A, lda, gather, top, (const bf16*)W, (bf16*)C, ldc, N, K, table, n_tiles, inter, act_limit, act_alpha);
     else
-      moe_gemm_mma_kernel<float, false><<<grid, 128, 0, stream>>>((const bf16*)A, lda, gather, top, (const bf16*)W, (float*)C, ldc, N, K, table, n_tiles, inter);
+      moe_gemm_mma_kernel<float, false><<<grid, 128, 0, stream>>>((const bf16*)A, lda, gather, top, (const bf16*)W, (float*)C, ldc, N, K, table, n_tiles, inter, act_limit, act_alpha);
     return launch_status();
   }
   dim3 grid(max_tiles, (N + FB - 1) / FB);
   if (a_bf16) {
     if (gated)
-      moe_gemm_fma_kernel<bf16, bf16, bf16, true><<<grid, 256, 0, stream>>>((const bf16*)A, lda, gather, top, (const bf16*)W, (bf16*)C, ldc, N, K, table, n_tiles, inter);
+      moe_gemm_fma_kernel<bf16, bf16, bf16, true><<<grid, 256, 0, stream>>>((const bf16*)A, lda, gather, top, (const bf16*)W, (bf16*)C, ldc, N, K, table, n_tiles, inter, act_limit, act_alpha);
     else
-      moe_gemm_fma_kernel<bf16, bf16, float, false><<<grid, 256, 0, stream>>>((const bf16*)A, lda, gather, top, (const bf16*)W, (float*)C, ldc, N, K, table, n_tiles, inter);
+      moe_gemm_fma_kernel<bf16, bf16, float, false><<<grid, 256, 0, stream>>>((const bf16*)A, lda, gather, top, (const bf16*)W, (float*)C, ldc, N, K, table, n_tiles, inter, act_limit, act_alpha);
   } else {
     if (gated)
-      moe_gemm_fma_kernel<float, float, float, true><<<grid, 256, 0, stream>>>((const float*)A, lda, gather, top, (const float*)W, (float*)C, ldc, N, K, table, n_tiles, inter);
+      moe_gemm_fma_kernel<float, float, float, true><<<grid, 256, 0, stream>>>((const float*)A, lda, gather, top, (const float*)W, (float*)C, ldc, N, K, table, n_tiles, inter, act_limit, act_alpha);
     else
-      moe_gemm_fma_kernel<float, float, float, false><<<grid, 256, 0, stream>>>((const float*)A, lda, gather, top, (const float*)W, (float*)C, ldc, N, K, table, n_tiles, inter);
+      moe_gemm_fma_kernel<float, float, float, false><<<grid, 256, 0, stream>>>((const float*)A, lda, gather, top, (const float*)W, (float*)C, ldc, N, K, table, n_tiles, inter, act_limit, act_alpha);
   }
   return launch_status();
 }

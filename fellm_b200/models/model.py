@@ -73,6 +73,20 @@ def _parallel(block, x, ctx, cache, act_dtype, reads_only):
         block.ffn.forward(h, ctx, x)
 
 
+@register_arrangement("parallel_gated")
+def _parallel_gated(block, x, ctx, cache, act_dtype, reads_only):
+    """h = norm1(x); x += mixer(h) * sigmoid(W_1 h + b_1) + ffn(h) * sigmoid(W_2 h + b_2): the sublayers add into rows of
+    zeros of their own, and the block's gates take those into the stream."""
+    if block.gate is None:
+        raise ConfigError("the 'parallel_gated' arrangement needs the layer's gates")
+    h = block.norm1.forward(x, act_dtype)
+    zg = block.gate.logits(h)
+    results = [block.mixer.forward(h, ctx, cache, torch.zeros_like(x), reads_only=reads_only)]
+    if block.ffn is not None:
+        results.append(block.ffn.forward(h, ctx, torch.zeros_like(x)))
+    block.gate.add(x, results, zg)
+
+
 def _with_children(part):
     return [part] + [q for c in part.children() for q in _with_children(c)]
 
@@ -90,15 +104,20 @@ class Block:
         self.mixer = build_part("mixer", spec.mixer, dtype)
         self.norm2 = build_part("norm", spec.norm2, dtype) if spec.norm2 is not None else None
         self.ffn = build_part("feed_forward", spec.ffn, dtype) if spec.ffn is not None else None
+        self.gate = build_part("gate", spec.gate, dtype) if spec.gate is not None else None
+        self.side = build_part("side", spec.side, dtype) if spec.side is not None else None
         self.norm_after = None
 
     def parts(self):
-        return [q for p in (self.norm1, self.mixer, self.norm2, self.ffn) if p is not None for q in _with_children(p)]
+        return [q for p in (self.norm1, self.mixer, self.norm2, self.ffn, self.gate, self.side) if p is not None
+                for q in _with_children(p)]
 
     def forward(self, x, ctx, cache, act_dtype, reads_only=False, norm_after=None):
         """x: float32 residual stream [T, d], updated in place."""
         self.norm_after = norm_after
         self.arrange(self, x, ctx, cache, act_dtype, reads_only)
+        if self.side is not None:
+            self.side.forward(x, ctx)
         return x
 
 
@@ -111,14 +130,16 @@ class Model:
         self.final_norm = build_part("norm", spec.final_norm, dtype)
         self.head = build_part("head", spec.head, dtype)
         self.connectors = [build_part("connector", cs, dtype) for cs in spec.connectors]
+        self.shared = [build_part("shared", ss, dtype) for ss in spec.shared]
         self.schedule = list(spec.schedule)
+        self.after_run = None          # a callable (schedule entry, x) that is shown the stream after every run (tests, debugging)
 
     # ---- parameters
     def all_parts(self):
         parts = [self.embedding]
         for b in self.blocks:
             parts += b.parts()
-        return parts + self.connectors + [self.final_norm, self.head]
+        return parts + self.connectors + self.shared + [self.final_norm, self.head]
 
     def param_table(self) -> Dict[str, tuple]:
         """{tensor name in the file: (part, local name, ParamDecl)} over all parts."""
@@ -151,6 +172,14 @@ class Model:
             part.bind(per_part.get(id(part), {}))
         if getattr(self.head, "tied", False):
             self.head.bind({"weight": self.embedding.w["weight"]})
+        # parts that read a shared part's tensors are handed it by the name of its first tensor
+        by_name = {sp.spec.tensor_name(next(iter(sp.param_decls()))): sp for sp in self.shared}
+        for part in self.all_parts():
+            want = getattr(part, "uses_shared", None)
+            if want is not None:
+                if want not in by_name:
+                    raise ConfigError(f"a part asks for the shared tensor {want!r}, which the model does not have")
+                part.attach(by_name[want])
 
     def kernel_modules(self):
         mods = []
@@ -195,6 +224,8 @@ class Model:
                 norm_after = self.final_norm if (ctx.logits_all and ctx.n_logit_rows) else None
             self.blocks[run.layer].forward(x, ctx, caches[src], self.act_dtype,
                                            reads_only=run.cache_of is not None, norm_after=norm_after)
+            if self.after_run is not None:
+                self.after_run(n, x)
         if ctx.n_logit_rows == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=x.device)
         if ctx.logits_all and getattr(self.head, "takes_lazy_norm", False):

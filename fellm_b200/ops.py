@@ -182,6 +182,82 @@ def concat_cast(a, b, out_dtype, out=None):
     return out
 
 
+def rmsnorm_groups(x, w, eps: float, groups: int, out_dtype, rows=None, out=None):
+    """RMSNorm in `groups` equal consecutive parts of the row, each over its own root mean square, then the weight:
+    x float32 [T, d], w float32 [d] -> [T or len(rows), d] in out_dtype."""
+    _dev(x, w, rows)
+    assert x.dtype == torch.float32 and w.dtype == torch.float32 and x.is_contiguous()
+    d = x.shape[-1]
+    assert w.numel() == d
+    if groups < 1 or d % groups:
+        raise KernelError(f"rmsnorm_groups: {groups} groups do not divide a row of {d}")
+    n = x.shape[0] if rows is None else rows.numel()
+    if rows is not None:
+        _i32(rows, "rows")
+    if out is None:
+        out = torch.empty((n, d), dtype=out_dtype, device=x.device)
+    f = _fn("elementwise", "fellm_rmsnorm_groups", [_c_p, _c_p, _c_p, _c_int, _c_p, _c_int, _c_int, _c_int, _c_f, _c_p])
+    _check(f(_p(x), _p(w), _p(out), _is_bf16(out), _p(rows), n, d, int(groups), float(eps), _stream()), "rmsnorm_groups")
+    return out
+
+
+def poly_norm(z, coef, eps: float, out_dtype, out=None):
+    """z float32 [T, F], coef float32 [4] = (a, b, c, e) -> a N(z) + b N(z^2) + c N(z^3) + e in out_dtype, powers
+    element by element, N = over the row's root mean square (eps under the root)."""
+    _dev(z, coef)
+    assert z.dtype == torch.float32 and z.is_contiguous() and coef.dtype == torch.float32 and coef.numel() == 4
+    T, F = z.shape
+    if out is None:
+        out = torch.empty((T, F), dtype=out_dtype, device=z.device)
+    f = _fn("elementwise", "fellm_poly_norm", [_c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_f, _c_p])
+    _check(f(_p(z), _p(coef), _p(out), _is_bf16(out), T, F, float(eps), _stream()), "poly_norm")
+    return out
+
+
+def gated_add(x, ys, zg):
+    """x float32 [T, d] += sum over the sublayers s of ys[s] * sigmoid(zg[:, s * d : (s + 1) * d]); ys: one or two
+    float32 [T, d]; zg float32 [T, >= len(ys) * d]: the gates' logits."""
+    _dev(x, zg, *ys)
+    T, d = x.shape
+    assert 1 <= len(ys) <= 2 and x.dtype == torch.float32 and x.is_contiguous() and zg.dtype == torch.float32
+    assert zg.stride(1) == 1 and zg.shape[1] >= len(ys) * d
+    for y in ys:
+        assert y.dtype == torch.float32 and y.is_contiguous() and y.shape == x.shape
+    residual_written(x)
+    f = _fn("elementwise", "fellm_gated_add", [_c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p])
+    _check(f(_p(x), _p(ys[0]), _p(ys[1]) if len(ys) > 1 else None, _p(zg), zg.stride(0), T, d, _stream()), "gated_add")
+    return x
+
+
+def token_side(x, tokens, table, offset: int, w_gate, w_proj, norm_w, eps: float, status=None):
+    """What a token adds to the stream by itself: e = table[token, offset : offset + m]; g = gelu_tanh(W_gate x) * e;
+    y = W_proj g; x += y / sqrt(mean(y^2) + eps) * norm_w.  x float32 [T, d] in place; W_gate [m, d], W_proj [d, m],
+    table [vocab, >= offset + m] of one dtype; float32 sums."""
+    _dev(x, tokens, table, w_gate, w_proj, norm_w)
+    _i32(tokens, "tokens")
+    T, d = x.shape
+    m = w_gate.shape[0]
+    assert x.dtype == torch.float32 and x.is_contiguous() and norm_w.dtype == torch.float32 and norm_w.numel() == d
+    assert w_gate.shape == (m, d) and w_proj.shape == (d, m) and w_gate.is_contiguous() and w_proj.is_contiguous()
+    assert table.dtype == w_gate.dtype == w_proj.dtype and table.stride(1) == 1 and 0 <= offset and offset + m <= table.shape[1]
+    residual_written(x)
+    f = _fn("elementwise", "fellm_token_side", [_c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p, _c_p, _c_int, _c_p, _c_int, _c_int,
+                                                _c_int, _c_f, _c_p, _c_p])
+    _check(f(_p(x), _p(tokens), _p(table), table.stride(0), int(offset), table.shape[0], _p(w_gate), _p(w_proj), _is_bf16(w_gate),
+             _p(norm_w), T, d, m, float(eps), _p(status), _stream()), "token_side")
+    return x
+
+
+def add_rows(x, y):
+    """x float32 += y float32 of the same shape."""
+    _dev(x, y)
+    assert x.dtype == torch.float32 and y.dtype == torch.float32 and x.is_contiguous() and y.is_contiguous() and x.shape == y.shape
+    residual_written(x)
+    f = _fn("elementwise", "fellm_add_rows", [_c_p, _c_p, _c_ll, _c_p])
+    _check(f(_p(x), _p(y), x.numel(), _stream()), "add_rows")
+    return x
+
+
 # ------------------------------------------------------------------------------ matrix products
 
 def gemm_simt(a, w, bias=None, out=None, out_dtype=None, accumulate=False):
@@ -208,6 +284,25 @@ def gemm_simt(a, w, bias=None, out=None, out_dtype=None, accumulate=False):
              _c_int, _c_p])
     _check(f(_p(a), _is_bf16(a), _p(w), _is_bf16(w), _p(bias), _p(out), _is_bf16(out), M, N, K,
              a.stride(0), w.stride(0), out.stride(0), int(accumulate), _stream()), "gemm_simt")
+    return out
+
+
+def head_gemm(a, w, out, *, a_head: int, out_head: int):
+    """One product per head in one launch, float32 FMA: out[t, h * out_head + n] = sum_k a[t, h * a_head + k] w[h, n, k]
+    for h < H, n < N, k < K (w [H, N, K] contiguous; a and out are row-major with the heads side by side in a row,
+    a head's block starting every a_head / out_head columns and possibly wider than K / N).  Every output is one
+    k-ordered chain: a row's result does not depend on the batch.  Any mix of bfloat16 / float32."""
+    _dev(a, w, out)
+    H, N, K = w.shape
+    T = a.shape[0]
+    assert w.is_contiguous() and a.stride(1) == 1 and out.stride(1) == 1 and out.shape[0] == T
+    assert a.shape[1] >= (H - 1) * a_head + K and out.shape[1] >= (H - 1) * out_head + N
+    if _is_bf16(out) and not _is_bf16(a):
+        raise KernelError("head_gemm: float32 activations do not round down to a bfloat16 result")
+    f = _fn("gemm_simt", "fellm_gemm_simt_batched", [_c_p, _c_int, _c_p, _c_int, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                                     _c_int, _c_int, _c_ll, _c_ll, _c_ll, _c_p])
+    _check(f(_p(a), _is_bf16(a), _p(w), _is_bf16(w), _p(out), _is_bf16(out), H, T, N, K, a.stride(0), K, out.stride(0),
+             int(a_head), N * K, int(out_head), _stream()), "head_gemm")
     return out
 
 
@@ -575,20 +670,32 @@ def moe_route(logits, E: int, top: int, renormalize: bool = False):
     return idx, w
 
 
-def moe_router(h, w_router, top: int, renormalize: bool = False):
+def moe_router(h, w_router, top: int, renormalize: bool = False, *, score: str = "softmax", correction=None,
+               groups=None):
     """The router's product and the routing in one launch: z = h W_router^T in float32 (h [T, K] and W_router [E, K]
-    bfloat16 or float32), then as moe_route.  Returns (idx int32 [T, top], w float32 [T, top])."""
-    _dev(h, w_router)
+    bfloat16 or float32), then as moe_route.  score = "sigmoid": the scores are sigmoid(z); the choice looks at
+    score + correction (float32 [E]) and, with groups = (count, keep, best), only inside the `keep` of `count` equal
+    groups of neighbouring experts whose `best` largest choice scores sum highest; the weights are the plain scores
+    (renormalize: over their sum + 1e-20).  Returns (idx int32 [T, top], w float32 [T, top])."""
+    _dev(h, w_router, correction)
     assert h.stride(1) == 1 and w_router.is_contiguous() and h.shape[1] == w_router.shape[1]
     T, K = h.shape
     E = w_router.shape[0]
     if not 1 <= top <= min(E, MOE_MAX_TOP):
         raise KernelError(f"moe_router: top {top} must be in 1..{min(E, MOE_MAX_TOP)}")
+    if score not in ("softmax", "sigmoid"):
+        raise KernelError(f"moe_router: unknown score {score!r}")
+    if score == "softmax" and (correction is not None or groups):
+        raise KernelError("moe_router: a correction and groups go with sigmoid scores")
+    n_groups, keep, best = groups if groups else (1, 1, 1)
+    if correction is not None:
+        assert correction.dtype == torch.float32 and correction.numel() == E and correction.is_contiguous()
     idx = torch.empty((T, top), dtype=torch.int32, device=h.device)
     w = torch.empty((T, top), dtype=torch.float32, device=h.device)
-    f = _fn("moe", "fellm_moe_router", [_c_p, _c_int, _c_int, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p, _c_p, _c_p])
+    f = _fn("moe", "fellm_moe_router", [_c_p, _c_int, _c_int, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p, _c_p,
+                                        _c_int, _c_p, _c_int, _c_int, _c_int, _c_p])
     _check(f(_p(h), _is_bf16(h), h.stride(0), _p(w_router), _is_bf16(w_router), T, K, E, top, int(renormalize), _p(idx),
-             _p(w), _stream()), "moe_router")
+             _p(w), int(score == "sigmoid"), _p(correction), int(n_groups), int(keep), int(best), _stream()), "moe_router")
     return idx, w
 
 
@@ -626,11 +733,12 @@ def moe_plan(idx, E: int, row_tile: int = MOE_ROW_TILE) -> MoePlan:
     return plan
 
 
-def moe_gemm(a, w, plan: MoePlan, *, gated: bool, gather: bool, interleaved: bool = False):
+def moe_gemm(a, w, plan: MoePlan, *, gated: bool, gather: bool, interleaved: bool = False, act=None):
     """Grouped product over a plan's row tiles.  w [E, (2 if gated else 1) * N, K]; gather: row r of the result
     reads a[token of the pair sorted r] (a [T, K]); else a [P, K] is in sorted order.  gated: SiLU(gate) * up in
     a's dtype (w's rows: gate rows then up rows, or, interleaved, blocks of 8 gate and 8 up rows by turns); else
-    float32.  Returns [P, N] in sorted order.
+    float32.  act = (limit, alpha): the gated activation is the clamped form min(g, limit) sigmoid(alpha min(g, limit))
+    (clamp(u, -limit, limit) + 1) instead.  Returns [P, N] in sorted order.
     bfloat16: tcgen05 (tiles of 128 rows, the plan made for them), a warp a column for a handful of pairs, mma.sync
     tiles of 64 rows between; float32, or sizes those do not take: float32 FMA."""
     _dev(a, w)
@@ -640,6 +748,9 @@ def moe_gemm(a, w, plan: MoePlan, *, gated: bool, gather: bool, interleaved: boo
     assert a.shape[1] == K
     P = plan.pairs
     out = torch.empty((P, N), dtype=a.dtype if gated else torch.float32, device=a.device)
+    act_limit, act_alpha = (float(act[0]), float(act[1])) if act else (0.0, 1.0)
+    if act and not act_limit > 0.0:
+        raise KernelError("moe_gemm: the clamped activation needs a positive limit")
     bf = a.dtype == torch.bfloat16
     if (bf and plan.row_tile == MOE_UMMA_ROW_TILE and K % 8 == 0 and (not gated or (interleaved and N % 8 == 0))
             and w.data_ptr() % 16 == 0):
@@ -650,17 +761,18 @@ def moe_gemm(a, w, plan: MoePlan, *, gated: bool, gather: bool, interleaved: boo
             a = rows
         assert a.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0
         f = _fn("gemm_umma", "fellm_gemm_umma_grouped", [_c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
-                                                         _c_p, _c_p, _c_int, _c_p, _c_p])
+                                                         _c_p, _c_p, _c_int, _c_p, _c_f, _c_f, _c_p])
         _check(f(_p(a), _p(w), _p(out), _EPI_SWIGLU if gated else _EPI_F32, P, n_rows, K, E, a.stride(0), out.stride(0),
-                 _p(plan.table), _p(plan.n_tiles), plan.max_tiles, _p(umma_status(a.device)), _stream()), "gemm_umma_grouped")
+                 _p(plan.table), _p(plan.n_tiles), plan.max_tiles, _p(umma_status(a.device)), act_limit, act_alpha, _stream()),
+               "gemm_umma_grouped")
         return out
     if plan.row_tile != MOE_ROW_TILE:
         raise KernelError(f"moe_gemm: a plan of {plan.row_tile}-row tiles needs the tcgen05 grouped product (bfloat16, K % 8 == 0)")
     f = _fn("moe", "fellm_moe_gemm", [_c_p, _c_int, _c_int, _c_p, _c_int, _c_p, _c_int, _c_p, _c_int, _c_int, _c_int, _c_int,
-                                      _c_int, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_p])
+                                      _c_int, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_f, _c_f, _c_p])
     _check(f(_p(a), _is_bf16(a), a.stride(0), _p(plan.sorted) if gather else None, plan.top, _p(w), _is_bf16(w), _p(out),
              _is_bf16(out), N, N, K, int(gated), _p(plan.table), _p(plan.n_tiles), plan.max_tiles, int(MOE_MMA),
-             int(interleaved), int(P <= MOE_FEW_PAIRS), _stream()), "moe_gemm")
+             int(interleaved), int(P <= MOE_FEW_PAIRS), act_limit, act_alpha, _stream()), "moe_gemm")
     return out
 
 
@@ -756,9 +868,12 @@ def kv_write(src, k_off, v_off, pool, block_table, positions, row_slot, layer, p
              _p(status), _stream()), "kv_write")
 
 
+ATTENTION_SIMT_MAX_HD = 1024       # the CUDA-core attention kernel's largest key (and value) size
+
+
 def paged_attention_general(q, H, hd, vd, pool, block_table, positions, row_slot, layer, page_tokens, G, scale, *,
                             window=None, chunk=None, softcap=None, gate=None, slopes=None, q_temp=None, warps=1, write_new=None,
-                            out=None):
+                            sinks=None, out_dim=None, out=None):
     """Attention on CUDA cores with float32 arithmetic for every form the part describes: q read in place from rows
     [T, >= H*hd] (heads at column 0), values of size vd, scores soft-capped (softcap * tanh(s / softcap)), keys limited
     to the last `window` positions and to the query's own block of `chunk` positions, and gate float32 [T, >= H]
@@ -768,13 +883,20 @@ def paged_attention_general(q, H, hd, vd, pool, block_table, positions, row_slot
     warps (1..8): how many warps share a (row, head)'s key tiles; a constant of the layer, since it sets the order of the sums.
     write_new = (k_off, v_off, status): a decode step (every row its request's only one): the rows' own keys and values,
     at those columns of q's rows, are read from there and written into their pages by this kernel (no kv_write in front).
-    Returns [T, H*vd] (H*hd when the values are the keys) in q's dtype."""
-    _dev(q, pool, block_table, positions, row_slot, gate, slopes)
+    sinks float32 [H]: exp(sinks[h]) joins head h's softmax denominator (no key, no value, not scaled).  out_dim (with
+    vd == 0): only the first out_dim elements of a key are read out as its value.
+    Returns [T, H*vd] (H*hd, or H*out_dim, when the values are the keys) in q's dtype."""
+    _dev(q, pool, block_table, positions, row_slot, gate, slopes, sinks)
+    if sinks is not None:
+        assert sinks.dtype == torch.float32 and sinks.numel() == H and sinks.is_contiguous()
+    od = int(out_dim or 0)
+    if od and (vd or od > hd):
+        raise KernelError(f"attention: a read-out of {od} elements needs values that are keys of at least that size")
     T = q.shape[0]
     if slopes is not None:
         assert slopes.dtype == torch.float32 and slopes.numel() == H and slopes.is_contiguous()
-    if hd > 256 or vd > 256:
-        raise KernelError(f"attention: head sizes {hd} / {vd} are above the kernel's maximum 256")
+    if hd > ATTENTION_SIMT_MAX_HD or vd > ATTENTION_SIMT_MAX_HD:
+        raise KernelError(f"attention: head sizes {hd} / {vd} are above the kernel's maximum {ATTENTION_SIMT_MAX_HD}")
     if H % G:
         raise KernelError(f"attention: {H} heads are not a multiple of {G} kv heads")
     assert q.stride(1) == 1 and pool.is_contiguous() and pool[0, 0].numel() == G * page_tokens * (hd + vd)
@@ -782,19 +904,58 @@ def paged_attention_general(q, H, hd, vd, pool, block_table, positions, row_slot
     if gate is not None:
         assert gate.dtype == torch.float32 and gate.stride(1) == 1
     if out is None:
-        out = torch.empty((T, H * (vd or hd)), dtype=q.dtype, device=q.device)
+        out = torch.empty((T, H * (vd or od or hd)), dtype=q.dtype, device=q.device)
     qt_coef, qt_every = q_temp if q_temp else (0.0, 0)
     f = _fn("attention_simt", "fellm_paged_attention_general",
             [_c_p, _c_int, _c_p, _c_int, _c_p, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int,
              _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _c_f, _c_int, _c_p, _c_int, _c_p, _c_f, _c_int, _c_int, _c_int,
-             _c_int, _c_p, _c_p])
+             _c_int, _c_p, _c_p, _c_int, _c_p])
     nk, nv, status = write_new if write_new else (-1, -1, None)
     _check(f(_p(q), _is_bf16(q), _p(pool), _is_bf16(pool), _p(block_table), block_table.shape[1],
              _p(positions), _p(row_slot), _p(out), T, H, G, hd, page_tokens, layer, pool.shape[1],
              float(scale), int(window or 0), vd, q.stride(0), float(softcap or 0.0), int(chunk or 0), _p(gate),
              gate.stride(0) if gate is not None else 0, _p(slopes), float(qt_coef), int(qt_every), int(warps), int(nk), int(nv),
-             _p(status), _stream()), "paged_attention_general")
+             _p(status), _p(sinks), od, _stream()), "paged_attention_general")
     return out
+
+
+def latent_prep(z, q_off, rq, c_off, rk, r_off, dr, wq, wc, eps, freq, n_rot, mag, positions, row_slot, cache, out_dtype,
+                status=None):
+    """A latent-attention layer's down projections z float32 [T, >= ...] -> the normed query latent [T, rq] in out_dtype
+    (returned), and into the token's cache row the normed key-value latent (rk) followed by the rotated key part (dr;
+    pairs (2i, 2i+1) of its first n_rot elements, angle = position * freq[i], cos and sin times mag).  cache: a
+    PagedView whose page-layer record is [page_tokens][rk + dr]."""
+    _dev(z, wq, wc, freq, positions, row_slot, cache.pool, cache.block_table)
+    assert z.dtype == torch.float32 and z.stride(1) == 1 and wq.dtype == torch.float32 and wc.dtype == torch.float32
+    assert wq.numel() == rq and wc.numel() == rk
+    pool = cache.pool
+    assert pool.is_contiguous() and pool[0, 0].numel() == cache.page_tokens * (rk + dr)
+    _i32(positions, "positions"), _i32(row_slot, "row_slot"), _i32(cache.block_table, "block_table")
+    T = z.shape[0]
+    cq = torch.empty((T, rq), dtype=out_dtype, device=z.device)
+    if _is_bf16(cq) != _is_bf16(pool):
+        raise KernelError("latent_prep: the cache and the activations are of one dtype")
+    f = _fn("latent", "fellm_latent_prep", [_c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p, _c_p, _c_f, _c_p,
+                                            _c_int, _c_f, _c_p, _c_p, _c_p, _c_int, _c_p, _c_int, _c_int, _c_int, _c_int, _c_p,
+                                            _c_int, _c_p, _c_p])
+    _check(f(_p(z), z.stride(0), q_off, rq, c_off, rk, r_off, dr, _p(wq), _p(wc), float(eps), _p(freq), int(n_rot), float(mag),
+             _p(positions), _p(row_slot), _p(cache.block_table), cache.block_table.shape[1], _p(pool), _is_bf16(pool),
+             cache.page_tokens, cache.layer, pool.shape[1], _p(cq), T, _p(status), _stream()), "latent_prep")
+    return cq
+
+
+def latent_rotate_q(q, H, dn, dr, q_abs, rk, freq, n_rot, mag, positions):
+    """The rotated part of every head's query (dr elements behind the dn unrotated ones of q [T, H * (dn + dr)]), rotated
+    by the row's position, into elements [rk, rk + dr) of the head's row of q_abs [T, H * (rk + dr)]."""
+    _dev(q, q_abs, freq, positions)
+    assert q.stride(1) == 1 and q_abs.is_contiguous() and q.dtype == q_abs.dtype
+    assert q.shape[1] >= H * (dn + dr) and q_abs.shape[1] == H * (rk + dr)
+    _i32(positions, "positions")
+    f = _fn("latent", "fellm_latent_rotate_q", [_c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p, _c_int, _c_p, _c_int, _c_f, _c_p,
+                                                _c_int, _c_p])
+    _check(f(_p(q), _is_bf16(q), q.stride(0), H, dn, dr, _p(q_abs), rk, _p(freq), int(n_rot), float(mag), _p(positions),
+             q.shape[0], _stream()), "latent_rotate_q")
+    return q_abs
 
 
 # ------------------------------------------------------------------------------ tensor-core products

@@ -1,6 +1,7 @@
-from . import (attention, connector, dyt, embedding, gated_delta, moe, parallel, retention, rmsnorm, rope,  # noqa: F401
-               shortconv, swiglu, timemix)                                                                        # (registers the parts)
+from . import (attention, connector, dyt, embedding, gated_delta, latent_attention, moe, parallel, polynorm,  # noqa: F401
+               residual_gate, retention, rmsnorm, rope, shortconv, swiglu, timemix, token_side)      # (registers the parts)
 from .base import (CONNECTORS, Connector, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS, Embedding,
-                   FeedForward, FixedState, Head, Mixer, Norm, PagedKV, ParamDecl, Part, PositionEncoding,
+                   FeedForward, FixedState, Head, Mixer, Norm, PagedKV, ParamDecl, Part, PositionEncoding, ResidualGate, Shared,
+                   SideInput,
                    build_part, register_part)
 from .spec import LayerSpec, ModelSpec, PartSpec, Run

@@ -176,6 +176,35 @@ class Connector(Part):
         raise NotImplementedError
 
 
+class ResidualGate(Part):
+    """Gates on what a block's sublayers add to the residual stream, computed from the sublayers' input."""
+
+    def logits(self, h: torch.Tensor) -> torch.Tensor:
+        """h [T, d], the sublayers' input -> float32 [T, n d], the gates' logits of the n sublayers side by side."""
+        raise NotImplementedError
+
+    def add(self, x: torch.Tensor, results, zg: torch.Tensor) -> torch.Tensor:
+        """x float32 [T, d] += the sublayers' float32 results, each through its gate."""
+        raise NotImplementedError
+
+
+class SideInput(Part):
+    """Something a token adds to the residual stream by itself after a block (read from the step's token ids, not from
+    other tokens): forward(x, ctx) updates the float32 rows x in place.  `uses_shared`: the tensor name of a shared
+    part of the model (ModelSpec.shared) that attach() is handed once, after every part is bound."""
+    uses_shared = None
+
+    def attach(self, shared: "Shared"):
+        pass
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Shared(Part):
+    """A part that owns tensors several other parts read (a table with a slice per layer)."""
+
+
 class Embedding(Part):
     def forward(self, tokens: torch.Tensor) -> torch.Tensor:
         """tokens int32 [T] -> float32 [T, d]."""
@@ -203,9 +232,13 @@ POSITION_ENCODINGS: Dict[str, type] = {}
 EMBEDDINGS: Dict[str, type] = {}
 HEADS: Dict[str, type] = {}
 CONNECTORS: Dict[str, type] = {}
+RESIDUAL_GATES: Dict[str, type] = {}
+SIDE_INPUTS: Dict[str, type] = {}
+SHARED: Dict[str, type] = {}
 
 _TABLES = {"mixer": MIXERS, "feed_forward": FEED_FORWARDS, "norm": NORMS,
-           "position": POSITION_ENCODINGS, "embedding": EMBEDDINGS, "head": HEADS, "connector": CONNECTORS}
+           "position": POSITION_ENCODINGS, "embedding": EMBEDDINGS, "head": HEADS, "connector": CONNECTORS,
+           "gate": RESIDUAL_GATES, "side": SIDE_INPUTS, "shared": SHARED}
 
 
 def register_part(category: str, kind: str):

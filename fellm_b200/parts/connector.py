@@ -4,7 +4,10 @@
 pass that starts: the entry of a pass of a looped run of layers (the same weights run several
 times in a row, each pass with caches of its own).
 
-'add_step': x <- x + step[t]: the same entry without a projection and without the embedding."""
+'add_step': x <- x + step[t]: the same entry without a projection and without the embedding.
+
+'add_embedding': x <- x + x0: the embedding's output added again; it owns no tensor and does nothing before the first
+pass."""
 from __future__ import annotations
 
 import torch
@@ -45,6 +48,19 @@ class AddStep(Connector):
 
     def forward(self, x, x0, step, act_dtype):
         return ops.add_row_vector(x, self.w["step"][step])
+
+    def kernel_modules(self, dtype):
+        return [("elementwise", None)]
+
+
+@register_part("connector", "add_embedding")
+class AddEmbedding(Connector):
+    def __init__(self, *, dtype: str, size: int):
+        super().__init__()
+        self.size = int(size)
+
+    def forward(self, x, x0, step, act_dtype):
+        return x if step == 0 else ops.add_rows(x, x0)
 
     def kernel_modules(self, dtype):
         return [("elementwise", None)]

@@ -5,6 +5,12 @@
     weights = their scores as they are (renormalize=True: divided by their sum)
     out = sum over the chosen experts, in the order of their scores, of weight * W_down (SiLU(W_gate h) * (W_up h))
 
+With score="sigmoid" the scores are s = sigmoid(z); the choice is made on s + correction (a tensor of the layer), and
+with groups=(count, keep, best) only inside the `keep` of `count` equal groups of neighbouring experts whose `best`
+largest choice scores sum highest; the weights stay the plain s (renormalize: over their sum).  With
+act=("clamped", limit, alpha) an expert computes min(g, limit) sigmoid(alpha min(g, limit)) (clamp(u, -limit, limit) + 1)
+in place of SiLU(g) u.
+
 Experts have no biases.  Nothing goes through the host: the router's choices are sorted by expert on the device
 (ops.moe_plan; the router's product and the routing are one launch, ops.moe_router) and two grouped products walk
 the sorted rows (tcgen05 for steps of many rows, mma.sync tiles between, a warp a column for a handful of tokens), the first gathering its input rows by token and
@@ -23,13 +29,34 @@ from .linear import linear_modules
 
 @register_part("feed_forward", "moe")
 class RoutedExperts(FeedForward):
-    def __init__(self, *, dtype: str, size: int, ff: int, experts: int, top: int, renormalize: bool = False):
+    def __init__(self, *, dtype: str, size: int, ff: int, experts: int, top: int, renormalize: bool = False,
+                 score: str = "softmax", correction: bool = False, groups=None, act=None):
         super().__init__()
         self.size, self.ff, self.E, self.top = int(size), int(ff), int(experts), int(top)
         self.renormalize = bool(renormalize)
         if not 1 <= self.top <= min(self.E, ops.MOE_MAX_TOP):
             raise ConfigError(f"moe: top {self.top} must be in 1..{min(self.E, ops.MOE_MAX_TOP)} ({self.E} experts)")
+        if score not in ("softmax", "sigmoid"):
+            raise ConfigError(f"moe: unknown score {score!r} (softmax, sigmoid)")
+        if score == "softmax" and (correction or groups):
+            raise ConfigError("moe: a correction of the choice and groups of experts go with sigmoid scores")
+        self.score, self.groups = score, None
+        if groups:
+            count, keep, best = (int(v) for v in groups)
+            if count < 1 or self.E % count or not 1 <= keep <= count or best < 1:
+                raise ConfigError(f"moe: {count} groups (keep {keep}) do not divide {self.E} experts")
+            if self.top > (self.E // count) * keep:
+                raise ConfigError(f"moe: top {self.top} is above the {(self.E // count) * keep} experts of {keep} groups")
+            self.groups = (count, keep, best)
+        self.act = None
+        if act:
+            kind, limit, alpha = act
+            if kind != "clamped" or not float(limit) > 0.0:
+                raise ConfigError(f"moe: unknown expert activation {act!r} (('clamped', limit > 0, alpha))")
+            self.act = (float(limit), float(alpha))
         self.decls = {"router.weight": ParamDecl((self.E, self.size), init=("normal", 0.5))}
+        if correction:
+            self.decls["correction"] = ParamDecl((self.E,), role="vector", init=("normal", 0.2))
         for e in range(self.E):
             self.decls[f"e{e}.gate.weight"] = ParamDecl((self.ff, self.size))
             self.decls[f"e{e}.up.weight"] = ParamDecl((self.ff, self.size))
@@ -51,13 +78,14 @@ class RoutedExperts(FeedForward):
 
     def forward(self, hn, ctx, out):
         w = self.w
-        idx, score = ops.moe_router(hn, w["router.weight"], self.top, self.renormalize)
+        idx, score = ops.moe_router(hn, w["router.weight"], self.top, self.renormalize, score=self.score,
+                                    correction=w.get("correction"), groups=self.groups)
         if hn.dtype != w["gate_up.weight"].dtype:          # a file that stores some experts in 32-bit under a bfloat16 engine
             hn = hn.to(w["gate_up.weight"].dtype)
         bf = hn.dtype == torch.bfloat16
         tile = ops.moe_row_tile(idx.numel(), bf, self.interleaved and self.ff % 8 == 0 and self.size % 8 == 0 and hn.stride(0) % 8 == 0)
         plan = ops.moe_plan(idx, self.E, tile)
-        a = ops.moe_gemm(hn, w["gate_up.weight"], plan, gated=True, gather=True, interleaved=self.interleaved)
+        a = ops.moe_gemm(hn, w["gate_up.weight"], plan, gated=True, gather=True, interleaved=self.interleaved, act=self.act)
         y = ops.moe_gemm(a, w["down.weight"], plan, gated=False, gather=False)
         ops.moe_combine(out, y, plan, score)
         return out

@@ -40,13 +40,19 @@ class LayerSpec:
     """One block.  `arrangement` names how the parts are wired, a key of
     fellm_b200.models.model.ARRANGEMENTS (`register_arrangement` adds one):
     'prenorm': h = x + mixer(norm1(x)); out = h + ffn(norm2(h))   (graph.rs:1650-1777).
+    'parallel': h = norm1(x); out = x + mixer(h) + ffn(h).
+    'parallel_gated': the same with each sublayer's result through the gates of `gate` on its way into the stream.
     norm1, norm2 and ffn may be None where an arrangement has no use for them (a layer without a
-    feed-forward, a block with one norm)."""
+    feed-forward, a block with one norm).  `gate` (category 'gate'): gates on the sublayers' results, for the
+    arrangements that use them.  `side` (category 'side'): what every token adds to the stream by itself after the
+    arrangement has run."""
     norm1: Optional[PartSpec]
     mixer: PartSpec
     norm2: Optional[PartSpec] = None
     ffn: Optional[PartSpec] = None
     arrangement: str = "prenorm"
+    gate: Optional[PartSpec] = None
+    side: Optional[PartSpec] = None
 
 
 @dataclass(frozen=True)
@@ -74,6 +80,7 @@ class ModelSpec:
     head: PartSpec
     schedule: List[Run] = field(default_factory=list)
     connectors: List[PartSpec] = field(default_factory=list)
+    shared: List[PartSpec] = field(default_factory=list)        # parts (category 'shared') whose tensors other parts read
 
     def __post_init__(self):
         if not self.schedule:
