@@ -349,12 +349,31 @@ def samusun_config(width, ff, layers, vocab):
                 norm=dict(eps=1e-5), layers=[dict(type=kinds[i % 4][0], mixer=kinds[i % 4][1], mlp=kinds[i % 4][2]) for i in range(layers)])
 
 
-DESIGNS = {"robazen": robazen_config, "samusun": samusun_config}
+def meresun_config(width, ff, layers, vocab):
+    """A Meresun model of real-looking layers at this width: latent attention with heads of 128 + 64 (unrotated + rotated)
+    and values of 128, one head per 128 of width, a key-value latent of 512, a query latent of 3/4 of the width, a window of
+    1,024 positions, frequencies scaled by 8 beyond 4,096 positions; feed-forwards by turns dense (`ff`, the polynomial
+    activation) and routed (8 experts of ff / 2 in 4 groups of which 2 are kept, two experts a token); gates on both
+    sublayers, a side input of 64 a token and layer, norms in 2 groups; no loop."""
+    H = max(width // 128, 1)
+    mix = dict(dim=128, heads=H, kv_rank=512, mask=dict(size=1024), q_rank=width * 3 // 4,
+               rot=dict(base=10000.0, dims=64, scaling=dict(factor=8.0, fast=32.0, original=4096, slow=1.0)), rot_dim=64,
+               scale=192 ** -0.5, vdim=128)
+    dense = dict(ff=ff, kind="dense")
+    moe = dict(expert=dict(ff=ff // 2, limit=7.0), kind="moe", router=dict(experts=8, groups=dict(count=4, keep=2), top=2))
+    return dict(architecture="Meresun", embedding=dict(scale=1.0), vocab=vocab, width=width, norm=dict(eps=1e-5, groups=2),
+                token_side=dict(dim=64),
+                layers=[dict(type="latent_attention", mixer=mix, mlp=moe if i % 2 else dense) for i in range(layers)])
+
+
+DESIGNS = {"robazen": robazen_config, "samusun": samusun_config, "meresun": meresun_config}
+# the model a design is measured beside (default: LFM2 of the same width, depth, feed-forward and vocabulary)
+BESIDE = {"meresun": "samusun"}
 
 
 def run_design(design, shapes, layers, batches, steps, warmup):
-    """Prefill and decode of the new design beside the LFM2 model of the same width, depth, feed-forward and
-    vocabulary (the closest model the engine has): random weights, the same measurements as the headline's."""
+    """Prefill and decode of the new design beside the closest model the engine has (BESIDE; else the LFM2 model) of the
+    same width, depth, feed-forward and vocabulary: random weights, the same measurements as the headline's."""
     import numpy as np
     import torch
     from fellm_b200.config import EngineOptions
@@ -367,7 +386,9 @@ def run_design(design, shapes, layers, batches, steps, warmup):
         lfm2["block_auto_adjust_ff_dim"] = False
         width, ff, vocab = lfm2["hidden_size"], lfm2["block_ff_dim"], lfm2["vocab_size"]
         row = {}
-        for name, cfg in ((design, DESIGNS[design](width, ff, layers, vocab)), ("lfm2", lfm2)):
+        beside = BESIDE.get(design)
+        other = ("lfm2", lfm2) if beside is None else (beside, DESIGNS[beside](width, ff, layers, vocab))
+        for name, cfg in ((design, DESIGNS[design](width, ff, layers, vocab)), other):
             ctx_end = PROMPT + warmup + steps + 80
             opts = EngineOptions(dtype="bfloat16", n_ctx=ctx_end, ctx_past_model=True, n_batch=4096, n_ubatch=2048,
                                  page_tokens=64, max_requests=max(batches), max_tokens=max(batches) * ctx_end, cuda_graphs=True)
@@ -538,8 +559,8 @@ def main():
                          "--context tokens each) to FILE and stop; not a bench value")
     ap.add_argument("--context", type=int, default=PROMPT)
     ap.add_argument("--design", choices=sorted(DESIGNS), default=None,
-                    help="prefill and decode throughput of this design at a few real-looking sizes beside the LFM2 model of "
-                         "equal width, depth and feed-forward (--layers layers, default 8; --steps decode steps, default 64); "
+                    help="prefill and decode throughput of this design at a few real-looking sizes beside the closest model of "
+                         "equal width, depth and feed-forward (LFM2; Samusun for meresun) (--layers layers, default 8; --steps decode steps, default 64); "
                          "prints one line of its own and leaves the headline measurement alone")
     args = ap.parse_args()
 

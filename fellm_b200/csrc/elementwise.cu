@@ -426,6 +426,147 @@ FELLM_API int fellm_token_side(float* x, const int* tokens, const void* table, i
                         (const float*)Wg, (const float*)Wp, w, d, m, eps, status);
 }
 
+// The same on tensor cores (bfloat16 tables, mma.sync.m16n8k16, float32 sums): a block takes 16 rows.  Its 8 warps
+// share the gate product's m outputs by tiles of 8 (the rows' x rounded to bfloat16 in shared memory, W_gate's
+// fragments read in place), g goes through shared memory as bfloat16, and each warp then owns d / 8 columns of
+// y = W_proj g, NT tiles of 8 in registers, so that a row's mean square is a sum over the warps and x is read and
+// written once.  A row's sums run in the same order whatever else the step holds.
+__device__ __forceinline__ void ts_ldsm_x4(unsigned* r, const void* smem) {
+  unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ts_mma16816(float* d, const unsigned* a, unsigned b0, unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <int NT>
+__global__ void __launch_bounds__(256)
+token_side_mma_kernel(float* __restrict__ x, const int* __restrict__ tokens, const bf16* __restrict__ table, int ldt, int off,
+                      int vocab, const bf16* __restrict__ Wg, const bf16* __restrict__ Wp, const float* __restrict__ w, int T,
+                      int d, int m, float eps, int* __restrict__ status) {
+  extern __shared__ __align__(16) unsigned char ts_smem[];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int ldx = d + 8, ldg = m + 8;                       // (16 bytes of padding a row spread the banks)
+  bf16* Xs = (bf16*)ts_smem;                               // [16][d + 8]
+  bf16* Gs = Xs + 16 * ldx;                                // [16][m + 8]
+  float* red = (float*)(Gs + 16 * ldg);                    // [8 warps][16 rows]
+  int* toks = (int*)(red + 128);                           // [16]
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
+  const int row0 = blockIdx.x * 16;
+  for (int i = tid; i < 16 * (d / 2); i += 256) {
+    const int r = i / (d / 2), k = 2 * (i - r * (d / 2));
+    float2 v = make_float2(0.f, 0.f);
+    if (row0 + r < T) v = *(const float2*)(x + (size_t)(row0 + r) * d + k);
+    *(__nv_bfloat162*)(Xs + r * ldx + k) = __floats2bfloat162_rn(v.x, v.y);
+  }
+  if (tid < 16) {
+    int tok = row0 + tid < T ? tokens[row0 + tid] : 0;
+    if (tok < 0 || tok >= vocab) { if (status) atomicExch(status, 1); tok = -1; }
+    toks[tid] = tok;
+  }
+  __syncthreads();
+  // g = gelu_tanh(x W_gate^T) * e
+  for (int nt = warp; nt < m / 8; nt += 8) {
+    float z[4] = {0.f, 0.f, 0.f, 0.f};
+    const bf16* wr = Wg + (size_t)(nt * 8 + g) * d + 2 * c;
+#pragma unroll 4
+    for (int ks = 0; ks < d / 16; ++ks) {
+      unsigned af[4];
+      ts_ldsm_x4(af, Xs + (lane & 15) * ldx + 16 * ks + 8 * (lane >> 4));
+      const unsigned b0 = *(const unsigned*)(wr + 16 * ks), b1 = *(const unsigned*)(wr + 16 * ks + 8);
+      ts_mma16816(z, af, b0, b1);
+    }
+    const int col = nt * 8 + 2 * c;
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      const int r = g + 8 * hf, tok = toks[r];
+      float e0 = 0.f, e1 = 0.f;
+      if (tok >= 0) { e0 = to_f(table[(size_t)tok * ldt + off + col]); e1 = to_f(table[(size_t)tok * ldt + off + col + 1]); }
+      *(__nv_bfloat162*)(Gs + r * ldg + col) = __floats2bfloat162_rn(gelu_tanh_f(z[2 * hf]) * e0, gelu_tanh_f(z[2 * hf + 1]) * e1);
+    }
+  }
+  __syncthreads();
+  // y = g W_proj^T: this warp's columns [warp d / 8, (warp + 1) d / 8)
+  const int n_tiles = d / 64, col0 = warp * (d / 8);
+  float acc[NT][4];
+#pragma unroll
+  for (int n = 0; n < NT; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+  for (int ks = 0; ks < m / 16; ++ks) {
+    unsigned af[4];
+    ts_ldsm_x4(af, Gs + (lane & 15) * ldg + 16 * ks + 8 * (lane >> 4));
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+      if (n < n_tiles) {
+        const bf16* pr = Wp + (size_t)(col0 + 8 * n + g) * m + 16 * ks + 2 * c;
+        ts_mma16816(acc[n], af, *(const unsigned*)pr, *(const unsigned*)(pr + 8));
+      }
+    }
+  }
+  float ss0 = 0.f, ss1 = 0.f;
+#pragma unroll
+  for (int n = 0; n < NT; ++n) {
+    ss0 = fmaf(acc[n][0], acc[n][0], fmaf(acc[n][1], acc[n][1], ss0));
+    ss1 = fmaf(acc[n][2], acc[n][2], fmaf(acc[n][3], acc[n][3], ss1));
+  }
+  ss0 += __shfl_xor_sync(0xffffffffu, ss0, 1); ss0 += __shfl_xor_sync(0xffffffffu, ss0, 2);
+  ss1 += __shfl_xor_sync(0xffffffffu, ss1, 1); ss1 += __shfl_xor_sync(0xffffffffu, ss1, 2);
+  if (c == 0) { red[warp * 16 + g] = ss0; red[warp * 16 + g + 8] = ss1; }
+  __syncthreads();
+  float t0 = 0.f, t1 = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { t0 += red[i * 16 + g]; t1 += red[i * 16 + g + 8]; }
+  const float sc0 = 1.0f / sqrtf(t0 / (float)d + eps), sc1 = 1.0f / sqrtf(t1 / (float)d + eps);
+#pragma unroll
+  for (int n = 0; n < NT; ++n) {
+    if (n < n_tiles) {
+      const int col = col0 + 8 * n + 2 * c;
+      const float2 wv = *(const float2*)(w + col);
+      if (row0 + g < T) {
+        float2* px = (float2*)(x + (size_t)(row0 + g) * d + col);
+        float2 v = *px; v.x += (acc[n][0] * sc0) * wv.x; v.y += (acc[n][1] * sc0) * wv.y; *px = v;
+      }
+      if (row0 + g + 8 < T) {
+        float2* px = (float2*)(x + (size_t)(row0 + g + 8) * d + col);
+        float2 v = *px; v.x += (acc[n][2] * sc1) * wv.x; v.y += (acc[n][3] * sc1) * wv.y; *px = v;
+      }
+    }
+  }
+}
+
+template <int NT>
+static int launch_token_side_mma(float* x, const int* tokens, const bf16* table, int ldt, int off, int vocab, const bf16* Wg,
+                                 const bf16* Wp, const float* w, int rows, int d, int m, float eps, int* status,
+                                 cudaStream_t stream) {
+  const size_t smem = (size_t)16 * (d + 8) * 2 + (size_t)16 * (m + 8) * 2 + 128 * sizeof(float) + 16 * sizeof(int);
+  auto kern = token_side_mma_kernel<NT>;
+  if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  return launch_k_class(launch_class_for_rows(rows, 0), kern, dim3((rows + 15) / 16), dim3(256), smem, stream, 1, x, tokens, table,
+                        ldt, off, vocab, Wg, Wp, w, rows, d, m, eps, status);
+}
+
+// bfloat16 tables; d a multiple of 64 up to 2048, m a multiple of 16 up to 512, tables that start on 4 bytes
+FELLM_API int fellm_token_side_mma(float* x, const int* tokens, const void* table, int ldt, int off, int vocab, const void* Wg,
+                                   const void* Wp, const float* w, int rows, int d, int m, float eps, int* status,
+                                   cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (!x || !tokens || !table || !Wg || !Wp || !w) return FELLM_ERR_ARG;
+  if (d < 64 || d % 64 || d > 2048 || m < 16 || m % 16 || m > 512) return FELLM_ERR_SIZE;
+  if (((size_t)Wg | (size_t)Wp) & 3 || ((size_t)x | (size_t)w) & 7) return FELLM_ERR_ARG;
+  const int nt = d / 64;
+#define TS_LAUNCH(N_) return launch_token_side_mma<N_>(x, tokens, (const bf16*)table, ldt, off, vocab, (const bf16*)Wg, (const bf16*)Wp, w, rows, d, m, eps, status, stream)
+  if (nt <= 2) TS_LAUNCH(2);
+  if (nt <= 4) TS_LAUNCH(4);
+  if (nt <= 8) TS_LAUNCH(8);
+  if (nt <= 16) TS_LAUNCH(16);
+  TS_LAUNCH(32);
+#undef TS_LAUNCH
+}
+
 // ---------------------------------------------------------------- one stream added to another
 // x += y   (float32; the embedding's output added again where a pass of a looped run of layers opens)
 __global__ void add_rows_kernel(float* __restrict__ x, const float* __restrict__ y, long long n) {

@@ -40,8 +40,12 @@ __device__ __forceinline__ int swz(int row, int chunk) { return row * 4 + (chunk
 template <int EPI>
 __global__ void __launch_bounds__(TTHREADS)
 gemm_tiled_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, const float* __restrict__ bias,
-                  void* __restrict__ out, int M, int N, int K, int lda, int ldw, int ldo) {
+                  void* __restrict__ out, int M, int N, int K, int lda, int ldw, int ldo,
+                  long long sa = 0, long long sw = 0, long long so = 0) {
   FELLM_TRACE_SCOPE(TRACE_GEMM_TILED);
+  // member blockIdx.z of a batch: operands and result moved on by the batch's strides (elements)
+  A += blockIdx.z * sa; W += blockIdx.z * sw;
+  out = (EPI == EPI_STORE) ? (void*)((bf16*)out + blockIdx.z * so) : (void*)((float*)out + blockIdx.z * so);
   extern __shared__ __align__(16) unsigned char smem_raw[];
   uint4* sA = (uint4*)smem_raw;                            // [stage][128 rows * 4 chunks]
   uint4* sB = sA + TSTAGES * TBM * 4;
@@ -160,7 +164,24 @@ static int launch(const bf16* A, const bf16* W, const float* bias, void* out, in
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   dim3 grid(ceil_div(N, TBN), ceil_div(M, TBM));
-  kern<<<grid, TTHREADS, smem, stream>>>(A, W, bias, out, M, N, K, lda, ldw, ldo);
+  kern<<<grid, TTHREADS, smem, stream>>>(A, W, bias, out, M, N, K, lda, ldw, ldo, 0, 0, 0);
+  return launch_status();
+}
+
+// A batch of such products in one launch (the heads of a layer, each with a matrix of its own, on column blocks of
+// the same rows): member b computes C_b[M, N] = A_b[M, K] W_b[N, K]^T with A_b = A + b sa, W_b = W + b sw,
+// C_b = C + b sc (strides in elements; bfloat16 in and out).
+FELLM_API int fellm_gemm_tiled_batched(const void* A, const void* W, void* out, int batch, int M, int N, int K, int lda,
+                                       int ldw, int ldo, long long sa, long long sw, long long so, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || batch <= 0) return 0;
+  if (!A || !W || !out || K <= 0) return FELLM_ERR_ARG;
+  if ((K % 8) || (lda % 8) || (ldw % 8) || (sa % 8) || (sw % 8) || batch > 65535) return FELLM_ERR_SIZE;
+  size_t smem = (size_t)TSTAGES * (TBM + TBN) * 4 * sizeof(uint4);
+  auto kern = gemm_tiled_kernel<EPI_STORE>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  dim3 grid(ceil_div(N, TBN), ceil_div(M, TBM), batch);
+  kern<<<grid, TTHREADS, smem, stream>>>((const bf16*)A, (const bf16*)W, nullptr, out, M, N, K, lda, ldw, ldo, sa, sw, so);
   return launch_status();
 }
 

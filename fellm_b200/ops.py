@@ -241,6 +241,14 @@ def token_side(x, tokens, table, offset: int, w_gate, w_proj, norm_w, eps: float
     assert w_gate.shape == (m, d) and w_proj.shape == (d, m) and w_gate.is_contiguous() and w_proj.is_contiguous()
     assert table.dtype == w_gate.dtype == w_proj.dtype and table.stride(1) == 1 and 0 <= offset and offset + m <= table.shape[1]
     residual_written(x)
+    if (TOKEN_SIDE_MMA and _is_bf16(w_gate) and d % 64 == 0 and 64 <= d <= 2048 and m % 16 == 0 and 16 <= m <= 512
+            and w_gate.data_ptr() % 4 == 0 and w_proj.data_ptr() % 4 == 0):
+        # bfloat16 tables: 16 rows a block on tensor cores
+        f = _fn("elementwise", "fellm_token_side_mma", [_c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int,
+                                                        _c_int, _c_f, _c_p, _c_p])
+        _check(f(_p(x), _p(tokens), _p(table), table.stride(0), int(offset), table.shape[0], _p(w_gate), _p(w_proj), _p(norm_w),
+                 T, d, m, float(eps), _p(status), _stream()), "token_side (tensor cores)")
+        return x
     f = _fn("elementwise", "fellm_token_side", [_c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p, _c_p, _c_int, _c_p, _c_int, _c_int,
                                                 _c_int, _c_f, _c_p, _c_p])
     _check(f(_p(x), _p(tokens), _p(table), table.stride(0), int(offset), table.shape[0], _p(w_gate), _p(w_proj), _is_bf16(w_gate),
@@ -288,10 +296,11 @@ def gemm_simt(a, w, bias=None, out=None, out_dtype=None, accumulate=False):
 
 
 def head_gemm(a, w, out, *, a_head: int, out_head: int):
-    """One product per head in one launch, float32 FMA: out[t, h * out_head + n] = sum_k a[t, h * a_head + k] w[h, n, k]
+    """One product per head in one launch: out[t, h * out_head + n] = sum_k a[t, h * a_head + k] w[h, n, k]
     for h < H, n < N, k < K (w [H, N, K] contiguous; a and out are row-major with the heads side by side in a row,
-    a head's block starting every a_head / out_head columns and possibly wider than K / N).  Every output is one
-    k-ordered chain: a row's result does not depend on the batch.  Any mix of bfloat16 / float32."""
+    a head's block starting every a_head / out_head columns and possibly wider than K / N).  All bfloat16, with
+    blocks that start on 16 bytes: tensor cores (mma.sync tiles, float32 sums); else float32 FMA, any mix of
+    bfloat16 / float32.  A row's result does not depend on the batch."""
     _dev(a, w, out)
     H, N, K = w.shape
     T = a.shape[0]
@@ -299,11 +308,22 @@ def head_gemm(a, w, out, *, a_head: int, out_head: int):
     assert a.shape[1] >= (H - 1) * a_head + K and out.shape[1] >= (H - 1) * out_head + N
     if _is_bf16(out) and not _is_bf16(a):
         raise KernelError("head_gemm: float32 activations do not round down to a bfloat16 result")
+    if (_is_bf16(a) and _is_bf16(w) and _is_bf16(out) and K % 8 == 0 and a_head % 8 == 0 and a.stride(0) % 8 == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and HEAD_GEMM_MMA):
+        f = _fn("gemm_tiled", "fellm_gemm_tiled_batched", [_c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                                           _c_ll, _c_ll, _c_ll, _c_p])
+        _check(f(_p(a), _p(w), _p(out), H, T, N, K, a.stride(0), K, out.stride(0), int(a_head), N * K, int(out_head), _stream()),
+               "head_gemm (tensor cores)")
+        return out
     f = _fn("gemm_simt", "fellm_gemm_simt_batched", [_c_p, _c_int, _c_p, _c_int, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                                                      _c_int, _c_int, _c_ll, _c_ll, _c_ll, _c_p])
     _check(f(_p(a), _is_bf16(a), _p(w), _is_bf16(w), _p(out), _is_bf16(out), H, T, N, K, a.stride(0), K, out.stride(0),
              int(a_head), N * K, int(out_head), _stream()), "head_gemm")
     return out
+
+
+TOKEN_SIDE_MMA = os.environ.get("FELLM_B200_TOKEN_SIDE_MMA", "1") != "0"
+HEAD_GEMM_MMA = os.environ.get("FELLM_B200_HEAD_GEMM_MMA", "1") != "0"
 
 
 # ------------------------------------------------------------------------------ short convolution
@@ -956,6 +976,60 @@ def latent_rotate_q(q, H, dn, dr, q_abs, rk, freq, n_rot, mag, positions):
     _check(f(_p(q), _is_bf16(q), q.stride(0), H, dn, dr, _p(q_abs), rk, _p(freq), int(n_rot), float(mag), _p(positions),
              q.shape[0], _stream()), "latent_rotate_q")
     return q_abs
+
+
+LATENT_ATTENTION_MMA = os.environ.get("FELLM_B200_LATENT_ATTENTION_MMA", "1") != "0"
+LATENT_SINGLE_ROWS = 32        # up to this many (token, head) rows an item: the kernel's form for single tokens
+LATENT_MAX_SPLITS = 16
+
+
+def latent_attention_takes(q_abs, pool, rk: int, dr: int, page_tokens: int) -> bool:
+    """Whether the tensor-core kernel takes a latent-attention layer of these sizes: bfloat16 queries and cache, a
+    latent of a multiple of 32 up to 512, rows of a multiple of 16 elements, pages of a multiple of 64 tokens."""
+    return (LATENT_ATTENTION_MMA and q_abs.dtype == torch.bfloat16 and pool.dtype == torch.bfloat16 and rk % 32 == 0
+            and 32 <= rk <= 512 and dr >= 0 and (rk + dr) % 16 == 0 and page_tokens % 64 == 0)
+
+
+def latent_attention_modules(rk: int, dr: int):
+    return [("latent_attention_mma", {"LAT_RK": rk, "LAT_DR": dr})]
+
+
+def latent_attention(q_abs, H, rk, dr, pool, block_table, positions, row_slot, item_start, n_items, max_item_rows, max_len,
+                     layer, page_tokens, scale, *, window=None, sinks=None, out=None):
+    """Latent attention on tensor cores (bfloat16): q_abs [T, H * (rk + dr)] contiguous, the queries taken into the
+    cache rows' space; pool's page-layer record is [page_tokens][rk + dr]; rows of item i are
+    item_start[i]..item_start[i + 1] with consecutive positions.  A key's value is the first rk elements of its row.
+    sinks float32 [H]: exp(sinks[h]) joins head h's denominator.  max_len: the longest context of the step (it only
+    sizes the split of a single token's key walk).  Returns [T, H * rk]."""
+    _dev(q_abs, pool, block_table, positions, row_slot, item_start, sinks)
+    T = q_abs.shape[0]
+    assert latent_attention_takes(q_abs, pool, rk, dr, page_tokens)
+    assert q_abs.is_contiguous() and q_abs.shape[1] == H * (rk + dr) and pool.is_contiguous()
+    assert pool[0, 0].numel() == page_tokens * (rk + dr)
+    _i32(block_table, "block_table"), _i32(positions, "positions"), _i32(row_slot, "row_slot"), _i32(item_start, "item_start")
+    if sinks is not None:
+        assert sinks.dtype == torch.float32 and sinks.numel() == H and sinks.is_contiguous()
+    if out is None:
+        out = torch.empty((T, H * rk), dtype=torch.bfloat16, device=q_abs.device)
+    variant = 1 if max_item_rows * H <= LATENT_SINGLE_ROWS else 0
+    n_splits, scratch = 1, None
+    if variant == 1:
+        # few CTAs walk many keys: split the walk so that the SMs have work (a constant of the step's shape)
+        kt = 64 if rk % 64 == 0 else 32
+        longest = -(-int(max_len) // 1024) * 1024          # (a captured step serves contexts up to the next multiple of 1,024)
+        span = min(int(window), longest) if window else longest
+        tiles = span // kt + 2
+        ctas = n_items * (-(-max_item_rows * H // 16))
+        n_splits = max(1, min(tiles // 2, 148 // max(ctas, 1), LATENT_MAX_SPLITS))
+        if n_splits > 1:
+            scratch = torch.empty((T * H * n_splits * (rk + 2),), dtype=torch.float32, device=q_abs.device)
+    f = _fn("latent_attention_mma", "fellm_latent_attention_mma",
+            [_c_p, _c_p, _c_p, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int,
+             _c_int, _c_f, _c_int, _c_p, _c_int, _c_p], defines={"LAT_RK": rk, "LAT_DR": dr})
+    _check(f(_p(q_abs), _p(pool), _p(block_table), block_table.shape[1], _p(positions), _p(row_slot), _p(item_start),
+             int(n_items), int(max_item_rows), T, _p(out), _p(scratch), n_splits, H, page_tokens, layer, pool.shape[1],
+             float(scale), int(window or 0), _p(sinks), variant, _stream()), "latent_attention")
+    return out
 
 
 # ------------------------------------------------------------------------------ tensor-core products

@@ -102,9 +102,15 @@ class LatentAttention(Mixer):
         qa = torch.empty((T, H * (rk + dr)), dtype=q.dtype, device=q.device)
         ops.head_gemm(q, w["ukT.weight"], qa, a_head=dn + dr, out_head=rk + dr)
         ops.latent_rotate_q(q, H, dn, dr, qa, rk, self.position.inv_freq, self.n_rot, self.magnitude, ctx.positions)
-        a = ops.paged_attention_general(qa, H, rk + dr, 0, cache.pool, cache.block_table, ctx.positions, ctx.row_slot,
-                                        cache.layer, cache.page_tokens, 1, self.scale, window=self.window,
-                                        warps=self.simt_warps, sinks=w.get("sink"), out_dim=rk)
+        if ops.latent_attention_takes(qa, cache.pool, rk, dr, cache.page_tokens):
+            a = ops.latent_attention(qa, H, rk, dr, cache.pool, cache.block_table, ctx.positions, ctx.row_slot, ctx.item_start,
+                                     ctx.n_items, ctx.max_item_rows, ctx.max_len, cache.layer, cache.page_tokens, self.scale,
+                                     window=self.window, sinks=w.get("sink"))
+        else:
+            # the 32-bit engine, and sizes the tensor-core kernel does not take
+            a = ops.paged_attention_general(qa, H, rk + dr, 0, cache.pool, cache.block_table, ctx.positions, ctx.row_slot,
+                                            cache.layer, cache.page_tokens, 1, self.scale, window=self.window,
+                                            warps=self.simt_warps, sinks=w.get("sink"), out_dim=rk)
         o = torch.empty((T, H * dv), dtype=a.dtype, device=a.device)
         ops.head_gemm(a, w["uv.weight"], o, a_head=rk, out_head=dv)
         linear(o, w["o.weight"], out=out, accumulate=True)
@@ -114,4 +120,7 @@ class LatentAttention(Mixer):
         return [self.w["down.weight"], self.w["uq.weight"], self.w["o.weight"]]
 
     def kernel_modules(self, dtype):
-        return linear_modules(dtype) + [("latent", None), ("attention_simt", None)]
+        mods = linear_modules(dtype) + [("latent", None), ("attention_simt", None)]
+        if dtype == "bfloat16" and self.rk % 32 == 0 and 32 <= self.rk <= 512 and (self.rk + self.dr) % 16 == 0:
+            mods += ops.latent_attention_modules(self.rk, self.dr)
+        return mods

@@ -175,6 +175,27 @@ def distance(got, want) -> float:
 LIMIT = {"float32": 1e-4, "bfloat16": 6e-2}
 
 
+def row_distances(got, want) -> torch.Tensor:
+    """distance() row by row."""
+    got, want = got.double().cpu(), want.double().cpu()
+    got = got - got.mean(-1, keepdim=True)
+    want = want - want.mean(-1, keepdim=True)
+    return (got - want).pow(2).mean(-1).sqrt() / want.pow(2).mean().sqrt()
+
+
+def assert_close(got, want, dtype: str, times: float = 1.0, note=None):
+    """In 32-bit every row is within the limit.  In bfloat16 a router's close call may go the other way for a token
+    (its input is rounded), and experts that differ by design then move that row, and faintly the rows that read it, far
+    beyond rounding: nine rows in ten are within the limit and the median row within a third of it, which no fault of
+    a mechanism passes (a fault moves every row)."""
+    d = row_distances(got, want)
+    limit = LIMIT[dtype] * times
+    if dtype == "float32":
+        assert float(d.max()) < limit, (note, float(d.max()))
+    else:
+        assert float(torch.quantile(d, 0.9)) < limit and float(d.median()) < limit / 3, (note, float(torch.quantile(d, 0.9)), float(d.median()))
+
+
 def run_cuts(engine, req, toks, cuts):
     """Feeds toks in portions of the given sizes (the rest one by one) and returns the logits of every position."""
     from fellm_b200.engine import StepItem
