@@ -445,24 +445,46 @@ __device__ __forceinline__ void ts_mma16816(float* d, const unsigned* a, unsigne
 
 template <int NT>
 __global__ void __launch_bounds__(256)
-token_side_mma_kernel(float* __restrict__ x, const int* __restrict__ tokens, const bf16* __restrict__ table, int ldt, int off,
-                      int vocab, const bf16* __restrict__ Wg, const bf16* __restrict__ Wp, const float* __restrict__ w, int T,
-                      int d, int m, float eps, int* __restrict__ status) {
+token_side_mma_kernel(float* __restrict__ x, const float* __restrict__ y0, const float* __restrict__ y1,
+                      const float* __restrict__ zg, int ldz, const int* __restrict__ tokens, const bf16* __restrict__ table,
+                      int ldt, int off, int vocab, const bf16* __restrict__ Wg, const bf16* __restrict__ Wp,
+                      const float* __restrict__ w, int T, int d, int m, float eps, int* __restrict__ status) {
   extern __shared__ __align__(16) unsigned char ts_smem[];
   pdl_launch_dependents();
   pdl_wait();
   const int ldx = d + 8, ldg = m + 8;                       // (16 bytes of padding a row spread the banks)
+  constexpr int LDP = 72;
   bf16* Xs = (bf16*)ts_smem;                               // [16][d + 8]
   bf16* Gs = Xs + 16 * ldx;                                // [16][m + 8]
-  float* red = (float*)(Gs + 16 * ldg);                    // [8 warps][16 rows]
+  float* part = (float*)(Gs + 16 * ldg);                   // [8 warps][16 rows][64 + 8]: the warps' shares of a gate product
+  float* red = part + 8 * 16 * LDP;                        // [8 warps][16 rows]
   int* toks = (int*)(red + 128);                           // [16]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
   const int row0 = blockIdx.x * 16;
-  for (int i = tid; i < 16 * (d / 2); i += 256) {
-    const int r = i / (d / 2), k = 2 * (i - r * (d / 2));
-    float2 v = make_float2(0.f, 0.f);
-    if (row0 + r < T) v = *(const float2*)(x + (size_t)(row0 + r) * d + k);
+  // the rows of x, with what the layer's gated sublayers add taken in on the way (y0 != null): x is written back
+  // with it, and every product below reads the sum
+#pragma unroll 4
+  for (int i = tid; i < 16 * (d / 4); i += 256) {
+    const int r = i / (d / 4), k = 4 * (i - r * (d / 4));
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (row0 + r < T) {
+      float* px = x + (size_t)(row0 + r) * d + k;
+      v = *(const float4*)px;
+      if (y0) {
+        const float* gz = zg + (size_t)(row0 + r) * ldz + k;
+        const float4 a = *(const float4*)(y0 + (size_t)(row0 + r) * d + k), ga = *(const float4*)gz;
+        float4 s = make_float4(a.x / (1.0f + expf(-ga.x)), a.y / (1.0f + expf(-ga.y)), a.z / (1.0f + expf(-ga.z)), a.w / (1.0f + expf(-ga.w)));
+        if (y1) {
+          const float4 b = *(const float4*)(y1 + (size_t)(row0 + r) * d + k), gb = *(const float4*)(gz + d);
+          s.x += b.x / (1.0f + expf(-gb.x)); s.y += b.y / (1.0f + expf(-gb.y));
+          s.z += b.z / (1.0f + expf(-gb.z)); s.w += b.w / (1.0f + expf(-gb.w));
+        }
+        v.x += s.x; v.y += s.y; v.z += s.z; v.w += s.w;
+        *(float4*)px = v;
+      }
+    }
     *(__nv_bfloat162*)(Xs + r * ldx + k) = __floats2bfloat162_rn(v.x, v.y);
+    *(__nv_bfloat162*)(Xs + r * ldx + k + 2) = __floats2bfloat162_rn(v.z, v.w);
   }
   if (tid < 16) {
     int tok = row0 + tid < T ? tokens[row0 + tid] : 0;
@@ -470,48 +492,68 @@ token_side_mma_kernel(float* __restrict__ x, const int* __restrict__ tokens, con
     toks[tid] = tok;
   }
   __syncthreads();
-  // g = gelu_tanh(x W_gate^T) * e
-  for (int nt = warp; nt < m / 8; nt += 8) {
-    float z[4] = {0.f, 0.f, 0.f, 0.f};
-    const bf16* wr = Wg + (size_t)(nt * 8 + g) * d + 2 * c;
-#pragma unroll 4
-    for (int ks = 0; ks < d / 16; ++ks) {
+  // g = gelu_tanh(x W_gate^T) * e, 64 outputs at a time: warp w takes the k16 steps w, w + 8, ... of every output,
+  // the warps' shares are added in the order of the warps
+  for (int nc0 = 0; nc0 < m; nc0 += 64) {
+    const int ntc = min(8, (m - nc0) / 8);
+    float z[8][4];
+#pragma unroll
+    for (int n = 0; n < 8; ++n) z[n][0] = z[n][1] = z[n][2] = z[n][3] = 0.f;
+    for (int ks = warp; ks < d / 16; ks += 8) {
+      unsigned b[8][2];
+#pragma unroll
+      for (int n = 0; n < 8; ++n) {
+        const bf16* wr = Wg + (size_t)(nc0 + min(n, ntc - 1) * 8 + g) * d + 16 * ks + 2 * c;
+        b[n][0] = *(const unsigned*)wr; b[n][1] = *(const unsigned*)(wr + 8);
+      }
       unsigned af[4];
       ts_ldsm_x4(af, Xs + (lane & 15) * ldx + 16 * ks + 8 * (lane >> 4));
-      const unsigned b0 = *(const unsigned*)(wr + 16 * ks), b1 = *(const unsigned*)(wr + 16 * ks + 8);
-      ts_mma16816(z, af, b0, b1);
-    }
-    const int col = nt * 8 + 2 * c;
 #pragma unroll
-    for (int hf = 0; hf < 2; ++hf) {
-      const int r = g + 8 * hf, tok = toks[r];
-      float e0 = 0.f, e1 = 0.f;
-      if (tok >= 0) { e0 = to_f(table[(size_t)tok * ldt + off + col]); e1 = to_f(table[(size_t)tok * ldt + off + col + 1]); }
-      *(__nv_bfloat162*)(Gs + r * ldg + col) = __floats2bfloat162_rn(gelu_tanh_f(z[2 * hf]) * e0, gelu_tanh_f(z[2 * hf + 1]) * e1);
+      for (int n = 0; n < 8; ++n) ts_mma16816(z[n], af, b[n][0], b[n][1]);
     }
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+      *(float2*)(part + (warp * 16 + g) * LDP + 8 * n + 2 * c) = make_float2(z[n][0], z[n][1]);
+      *(float2*)(part + (warp * 16 + g + 8) * LDP + 8 * n + 2 * c) = make_float2(z[n][2], z[n][3]);
+    }
+    __syncthreads();
+    for (int i = tid; i < 16 * 64; i += 256) {
+      const int r = i >> 6, cl = i & 63;
+      if (cl < ntc * 8) {
+        float sum = 0.f;
+#pragma unroll
+        for (int ww = 0; ww < 8; ++ww) sum += part[(ww * 16 + r) * LDP + cl];
+        const int tok = toks[r];
+        const float e = tok >= 0 ? to_f(table[(size_t)tok * ldt + off + nc0 + cl]) : 0.f;
+        Gs[r * ldg + nc0 + cl] = __float2bfloat16_rn(gelu_tanh_f(sum) * e);
+      }
+    }
+    __syncthreads();
   }
-  __syncthreads();
-  // y = g W_proj^T: this warp's columns [warp d / 8, (warp + 1) d / 8)
+  // y = g W_proj^T: this warp's columns [warp d / 8, (warp + 1) d / 8), n_tiles tiles of 8 (tiles beyond them repeat the last)
   const int n_tiles = d / 64, col0 = warp * (d / 8);
   float acc[NT][4];
 #pragma unroll
   for (int n = 0; n < NT; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
   for (int ks = 0; ks < m / 16; ++ks) {
+    unsigned b[NT][2];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+      const bf16* pr = Wp + (size_t)(col0 + 8 * min(n, n_tiles - 1) + g) * m + 16 * ks + 2 * c;
+      b[n][0] = *(const unsigned*)pr; b[n][1] = *(const unsigned*)(pr + 8);
+    }
     unsigned af[4];
     ts_ldsm_x4(af, Gs + (lane & 15) * ldg + 16 * ks + 8 * (lane >> 4));
 #pragma unroll
-    for (int n = 0; n < NT; ++n) {
-      if (n < n_tiles) {
-        const bf16* pr = Wp + (size_t)(col0 + 8 * n + g) * m + 16 * ks + 2 * c;
-        ts_mma16816(acc[n], af, *(const unsigned*)pr, *(const unsigned*)(pr + 8));
-      }
-    }
+    for (int n = 0; n < NT; ++n) ts_mma16816(acc[n], af, b[n][0], b[n][1]);
   }
   float ss0 = 0.f, ss1 = 0.f;
 #pragma unroll
   for (int n = 0; n < NT; ++n) {
-    ss0 = fmaf(acc[n][0], acc[n][0], fmaf(acc[n][1], acc[n][1], ss0));
-    ss1 = fmaf(acc[n][2], acc[n][2], fmaf(acc[n][3], acc[n][3], ss1));
+    if (n < n_tiles) {
+      ss0 = fmaf(acc[n][0], acc[n][0], fmaf(acc[n][1], acc[n][1], ss0));
+      ss1 = fmaf(acc[n][2], acc[n][2], fmaf(acc[n][3], acc[n][3], ss1));
+    }
   }
   ss0 += __shfl_xor_sync(0xffffffffu, ss0, 1); ss0 += __shfl_xor_sync(0xffffffffu, ss0, 2);
   ss1 += __shfl_xor_sync(0xffffffffu, ss1, 1); ss1 += __shfl_xor_sync(0xffffffffu, ss1, 2);
@@ -521,44 +563,55 @@ token_side_mma_kernel(float* __restrict__ x, const int* __restrict__ tokens, con
 #pragma unroll
   for (int i = 0; i < 8; ++i) { t0 += red[i * 16 + g]; t1 += red[i * 16 + g + 8]; }
   const float sc0 = 1.0f / sqrtf(t0 / (float)d + eps), sc1 = 1.0f / sqrtf(t1 / (float)d + eps);
+  // (the loads of a few tiles first, then their sums and stores: the loads are in flight together)
+  constexpr int NB = NT < 4 ? NT : 4;
+  const bool in0 = row0 + g < T, in1 = row0 + g + 8 < T;
+  float* x0 = x + (size_t)(row0 + g) * d;
+  float* x1 = x + (size_t)(row0 + g + 8) * d;
 #pragma unroll
-  for (int n = 0; n < NT; ++n) {
-    if (n < n_tiles) {
-      const int col = col0 + 8 * n + 2 * c;
-      const float2 wv = *(const float2*)(w + col);
-      if (row0 + g < T) {
-        float2* px = (float2*)(x + (size_t)(row0 + g) * d + col);
-        float2 v = *px; v.x += (acc[n][0] * sc0) * wv.x; v.y += (acc[n][1] * sc0) * wv.y; *px = v;
-      }
-      if (row0 + g + 8 < T) {
-        float2* px = (float2*)(x + (size_t)(row0 + g + 8) * d + col);
-        float2 v = *px; v.x += (acc[n][2] * sc1) * wv.x; v.y += (acc[n][3] * sc1) * wv.y; *px = v;
+  for (int n0 = 0; n0 < NT; n0 += NB) {
+    float2 wv[NB], v0[NB], v1[NB];
+#pragma unroll
+    for (int j = 0; j < NB; ++j) {
+      const int col = col0 + 8 * min(n0 + j, n_tiles - 1) + 2 * c;
+      wv[j] = *(const float2*)(w + col);
+      v0[j] = in0 ? *(const float2*)(x0 + col) : make_float2(0.f, 0.f);
+      v1[j] = in1 ? *(const float2*)(x1 + col) : make_float2(0.f, 0.f);
+    }
+#pragma unroll
+    for (int j = 0; j < NB; ++j) {
+      const int n = n0 + j, col = col0 + 8 * n + 2 * c;
+      if (n < n_tiles) {
+        if (in0) *(float2*)(x0 + col) = make_float2(v0[j].x + (acc[n][0] * sc0) * wv[j].x, v0[j].y + (acc[n][1] * sc0) * wv[j].y);
+        if (in1) *(float2*)(x1 + col) = make_float2(v1[j].x + (acc[n][2] * sc1) * wv[j].x, v1[j].y + (acc[n][3] * sc1) * wv[j].y);
       }
     }
   }
 }
 
 template <int NT>
-static int launch_token_side_mma(float* x, const int* tokens, const bf16* table, int ldt, int off, int vocab, const bf16* Wg,
-                                 const bf16* Wp, const float* w, int rows, int d, int m, float eps, int* status,
-                                 cudaStream_t stream) {
-  const size_t smem = (size_t)16 * (d + 8) * 2 + (size_t)16 * (m + 8) * 2 + 128 * sizeof(float) + 16 * sizeof(int);
+static int launch_token_side_mma(float* x, const float* y0, const float* y1, const float* zg, int ldz, const int* tokens,
+                                 const bf16* table, int ldt, int off, int vocab, const bf16* Wg, const bf16* Wp, const float* w,
+                                 int rows, int d, int m, float eps, int* status, cudaStream_t stream) {
+  const size_t smem = (size_t)16 * (d + 8) * 2 + (size_t)16 * (m + 8) * 2 + (8 * 16 * 72 + 128) * sizeof(float) + 16 * sizeof(int);
   auto kern = token_side_mma_kernel<NT>;
   if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  return launch_k_class(launch_class_for_rows(rows, 0), kern, dim3((rows + 15) / 16), dim3(256), smem, stream, 1, x, tokens, table,
-                        ldt, off, vocab, Wg, Wp, w, rows, d, m, eps, status);
+  return launch_k_class(launch_class_for_rows(rows, 0), kern, dim3((rows + 15) / 16), dim3(256), smem, stream, 1, x, y0, y1, zg, ldz,
+                        tokens, table, ldt, off, vocab, Wg, Wp, w, rows, d, m, eps, status);
 }
 
-// bfloat16 tables; d a multiple of 64 up to 2048, m a multiple of 16 up to 512, tables that start on 4 bytes
-FELLM_API int fellm_token_side_mma(float* x, const int* tokens, const void* table, int ldt, int off, int vocab, const void* Wg,
-                                   const void* Wp, const float* w, int rows, int d, int m, float eps, int* status,
-                                   cudaStream_t stream) {
+// bfloat16 tables; d a multiple of 64 up to 2048, m a multiple of 16 up to 512, tables that start on 4 bytes.
+// y0 (and y1) float32 [rows, d] with zg float32 [rows, >= d (2 d)]: x += y0 sigmoid(zg[:, :d]) (+ y1 sigmoid(zg[:, d:2d]))
+// first, in the same launch (what gated_add does), and the side input is computed from that sum.
+FELLM_API int fellm_token_side_mma(float* x, const float* y0, const float* y1, const float* zg, int ldz, const int* tokens,
+                                   const void* table, int ldt, int off, int vocab, const void* Wg, const void* Wp, const float* w,
+                                   int rows, int d, int m, float eps, int* status, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  if (!x || !tokens || !table || !Wg || !Wp || !w) return FELLM_ERR_ARG;
+  if (!x || !tokens || !table || !Wg || !Wp || !w || (y0 && !zg) || (y1 && !y0)) return FELLM_ERR_ARG;
   if (d < 64 || d % 64 || d > 2048 || m < 16 || m % 16 || m > 512) return FELLM_ERR_SIZE;
-  if (((size_t)Wg | (size_t)Wp) & 3 || ((size_t)x | (size_t)w) & 7) return FELLM_ERR_ARG;
+  if ((((size_t)Wg | (size_t)Wp) & 3) || (((size_t)x | (size_t)y0 | (size_t)y1 | (size_t)zg) & 15) || ((size_t)w & 7) || (y0 && (ldz & 3))) return FELLM_ERR_ARG;
   const int nt = d / 64;
-#define TS_LAUNCH(N_) return launch_token_side_mma<N_>(x, tokens, (const bf16*)table, ldt, off, vocab, (const bf16*)Wg, (const bf16*)Wp, w, rows, d, m, eps, status, stream)
+#define TS_LAUNCH(N_) return launch_token_side_mma<N_>(x, y0, y1, zg, ldz, tokens, (const bf16*)table, ldt, off, vocab, (const bf16*)Wg, (const bf16*)Wp, w, rows, d, m, eps, status, stream)
   if (nt <= 2) TS_LAUNCH(2);
   if (nt <= 4) TS_LAUNCH(4);
   if (nt <= 8) TS_LAUNCH(8);

@@ -36,6 +36,7 @@ constexpr bool SWZ = (CPR % 8 == 0);                // rows of whole 128-byte li
 constexpr int ROWB = D * 2 + (SWZ ? 0 : 16);        // else 16 bytes of padding spread the banks
 constexpr int KS = D / 16;                          // k16 steps over a row
 constexpr float LOG2E = 1.4426950408889634f;
+constexpr int MAX_SPLITS = 64;                     // ranges a single token's key walk is split into, at most
 
 __device__ __forceinline__ int tile_off(int row, int chunk) {
   return row * ROWB + ((SWZ ? (chunk ^ (row & 7)) : chunk) << 4);
@@ -90,7 +91,8 @@ __global__ void __launch_bounds__(NG * NC * 32, 1) latent_attention_kernel(LatAr
   const int item = blockIdx.y, H = a.H;
   const int r_begin = a.item_start[item];
   const int n_rows = (a.item_start[item + 1] - r_begin) * H;
-  const int R0 = blockIdx.x * MQ;
+  // (an item's last rows see the most keys: their CTAs start first, the short walks of its first rows fill the tail)
+  const int R0 = (int)(gridDim.x - 1 - blockIdx.x) * MQ;
   if (R0 >= n_rows) return;
   const int rows_here = min(MQ, n_rows - R0);
   const int pos0 = a.positions[r_begin];
@@ -261,25 +263,29 @@ __global__ void __launch_bounds__(NG * NC * 32, 1) latent_attention_kernel(LatAr
 // 2^(m_s - m) + 2^(sink - m)), m = max_s m_s.  A block per (token, head) row.
 __global__ void __launch_bounds__(128) latent_merge_kernel(const float* __restrict__ scratch, bf16* __restrict__ out,
                                                            const float* __restrict__ sinks, int H, int n_splits) {
+  __shared__ float sm_m[MAX_SPLITS], sm_w[MAX_SPLITS];
   pdl_launch_dependents();
   pdl_wait();
   const size_t row = blockIdx.x;
   const float* base = scratch + row * n_splits * (RK + 2);
-  float m = -INFINITY;
-  for (int s = 0; s < n_splits; ++s) m = fmaxf(m, base[(size_t)s * (RK + 2) + RK]);
-  float L = 0.f;
-  for (int s = 0; s < n_splits; ++s) {
-    const float* r = base + (size_t)s * (RK + 2);
-    if (r[RK] > -INFINITY) L += r[RK + 1] * exp2f(r[RK] - m);
+  if (threadIdx.x < n_splits) {                    // every range's (m, l) at once
+    sm_m[threadIdx.x] = base[(size_t)threadIdx.x * (RK + 2) + RK];
+    sm_w[threadIdx.x] = base[(size_t)threadIdx.x * (RK + 2) + RK + 1];
   }
+  __syncthreads();
+  float m = -INFINITY;
+  for (int s = 0; s < n_splits; ++s) m = fmaxf(m, sm_m[s]);
+  float L = 0.f;
+  for (int s = 0; s < n_splits; ++s) L += sm_m[s] > -INFINITY ? sm_w[s] * exp2f(sm_m[s] - m) : 0.f;
   if (sinks) L += exp2f(sinks[row % H] * LOG2E - m);
   const float inv = 1.0f / L;
+  __syncthreads();
+  if (threadIdx.x < n_splits) sm_w[threadIdx.x] = sm_m[threadIdx.x] > -INFINITY ? exp2f(sm_m[threadIdx.x] - m) : 0.f;
+  __syncthreads();
   for (int e = threadIdx.x; e < RK; e += blockDim.x) {
     float acc = 0.f;
-    for (int s = 0; s < n_splits; ++s) {
-      const float* r = base + (size_t)s * (RK + 2);
-      if (r[RK] > -INFINITY) acc += r[e] * exp2f(r[RK] - m);
-    }
+#pragma unroll 4
+    for (int s = 0; s < n_splits; ++s) acc = fmaf(base[(size_t)s * (RK + 2) + e], sm_w[s], acc);
     out[row * RK + e] = __float2bfloat16_rn(acc * inv);
   }
 }
@@ -314,7 +320,7 @@ FELLM_API int fellm_latent_attention_mma(const void* q, const void* pool, const 
                                          const float* sinks, int variant, cudaStream_t stream) {
   if (n_items <= 0 || rows_total <= 0 || max_item_rows <= 0) return 0;
   if (!q || !pool || !block_table || !positions || !row_slot || !item_start || !out) return FELLM_ERR_ARG;
-  if (H < 1 || page_tokens < 1 || n_splits < 1 || n_splits > 65535 || (n_splits > 1 && (!scratch || variant == 0))) return FELLM_ERR_ARG;
+  if (H < 1 || page_tokens < 1 || n_splits < 1 || n_splits > MAX_SPLITS || (n_splits > 1 && (!scratch || variant == 0))) return FELLM_ERR_ARG;
   LatArgs a;
   a.q = (const bf16*)q; a.pool = (const bf16*)pool; a.block_table = block_table; a.max_pages = max_pages;
   a.positions = positions; a.row_slot = row_slot; a.item_start = item_start; a.out = (bf16*)out; a.scratch = scratch;

@@ -76,14 +76,23 @@ def _parallel(block, x, ctx, cache, act_dtype, reads_only):
 @register_arrangement("parallel_gated")
 def _parallel_gated(block, x, ctx, cache, act_dtype, reads_only):
     """h = norm1(x); x += mixer(h) * sigmoid(W_1 h + b_1) + ffn(h) * sigmoid(W_2 h + b_2): the sublayers add into rows of
-    zeros of their own, and the block's gates take those into the stream."""
+    zeros of their own (or write rows of their own), and the block's gates take those into the stream."""
     if block.gate is None:
         raise ConfigError("the 'parallel_gated' arrangement needs the layer's gates")
     h = block.norm1.forward(x, act_dtype)
     zg = block.gate.logits(h)
-    results = [block.mixer.forward(h, ctx, cache, torch.zeros_like(x), reads_only=reads_only)]
+    # (a sublayer that says `can_store` writes its result instead of adding it: no rows of zeros to make)
+    if getattr(block.mixer, "can_store", False):
+        results = [block.mixer.forward(h, ctx, cache, torch.empty_like(x), reads_only=reads_only, store=True)]
+    else:
+        results = [block.mixer.forward(h, ctx, cache, torch.zeros_like(x), reads_only=reads_only)]
     if block.ffn is not None:
-        results.append(block.ffn.forward(h, ctx, torch.zeros_like(x)))
+        if getattr(block.ffn, "can_store", False):
+            results.append(block.ffn.forward(h, ctx, torch.empty_like(x), store=True))
+        else:
+            results.append(block.ffn.forward(h, ctx, torch.zeros_like(x)))
+    if getattr(block.side, "takes_gated_add", False):
+        return results, zg          # the side input's kernel reads the stream anyway: it adds the gated results on its way in
     block.gate.add(x, results, zg)
 
 
@@ -115,8 +124,10 @@ class Block:
     def forward(self, x, ctx, cache, act_dtype, reads_only=False, norm_after=None):
         """x: float32 residual stream [T, d], updated in place."""
         self.norm_after = norm_after
-        self.arrange(self, x, ctx, cache, act_dtype, reads_only)
-        if self.side is not None:
+        pending = self.arrange(self, x, ctx, cache, act_dtype, reads_only)
+        if pending is not None:
+            self.side.forward(x, ctx, pending=pending)
+        elif self.side is not None:
             self.side.forward(x, ctx)
         return x
 

@@ -229,10 +229,11 @@ def gated_add(x, ys, zg):
     return x
 
 
-def token_side(x, tokens, table, offset: int, w_gate, w_proj, norm_w, eps: float, status=None):
+def token_side(x, tokens, table, offset: int, w_gate, w_proj, norm_w, eps: float, status=None, pending=None):
     """What a token adds to the stream by itself: e = table[token, offset : offset + m]; g = gelu_tanh(W_gate x) * e;
     y = W_proj g; x += y / sqrt(mean(y^2) + eps) * norm_w.  x float32 [T, d] in place; W_gate [m, d], W_proj [d, m],
-    table [vocab, >= offset + m] of one dtype; float32 sums."""
+    table [vocab, >= offset + m] of one dtype; float32 sums.  pending = (ys, zg): what gated_add(x, ys, zg) would add is
+    added first (in the same launch where the kernel can), and the side input is computed from that sum."""
     _dev(x, tokens, table, w_gate, w_proj, norm_w)
     _i32(tokens, "tokens")
     T, d = x.shape
@@ -244,11 +245,22 @@ def token_side(x, tokens, table, offset: int, w_gate, w_proj, norm_w, eps: float
     if (TOKEN_SIDE_MMA and _is_bf16(w_gate) and d % 64 == 0 and 64 <= d <= 2048 and m % 16 == 0 and 16 <= m <= 512
             and w_gate.data_ptr() % 4 == 0 and w_proj.data_ptr() % 4 == 0):
         # bfloat16 tables: 16 rows a block on tensor cores
-        f = _fn("elementwise", "fellm_token_side_mma", [_c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int,
-                                                        _c_int, _c_f, _c_p, _c_p])
-        _check(f(_p(x), _p(tokens), _p(table), table.stride(0), int(offset), table.shape[0], _p(w_gate), _p(w_proj), _p(norm_w),
-                 T, d, m, float(eps), _p(status), _stream()), "token_side (tensor cores)")
+        f = _fn("elementwise", "fellm_token_side_mma", [_c_p, _c_p, _c_p, _c_p, _c_int, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p, _c_p,
+                                                        _c_p, _c_int, _c_int, _c_int, _c_f, _c_p, _c_p])
+        y0 = y1 = zg = None
+        if pending is not None:
+            ys, zg = pending
+            _dev(zg, *ys)
+            assert 1 <= len(ys) <= 2 and zg.dtype == torch.float32 and zg.stride(1) == 1 and zg.shape[1] >= len(ys) * d
+            for y in ys:
+                assert y.dtype == torch.float32 and y.is_contiguous() and y.shape == x.shape
+            y0, y1 = ys[0], (ys[1] if len(ys) > 1 else None)
+        _check(f(_p(x), _p(y0), _p(y1), _p(zg), zg.stride(0) if zg is not None else 0, _p(tokens), _p(table), table.stride(0),
+                 int(offset), table.shape[0], _p(w_gate), _p(w_proj), _p(norm_w), T, d, m, float(eps), _p(status), _stream()),
+               "token_side (tensor cores)")
         return x
+    if pending is not None:
+        gated_add(x, pending[0], pending[1])
     f = _fn("elementwise", "fellm_token_side", [_c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p, _c_p, _c_int, _c_p, _c_int, _c_int,
                                                 _c_int, _c_f, _c_p, _c_p])
     _check(f(_p(x), _p(tokens), _p(table), table.stride(0), int(offset), table.shape[0], _p(w_gate), _p(w_proj), _is_bf16(w_gate),

@@ -193,6 +193,7 @@ class SideInput(Part):
     other tokens): forward(x, ctx) updates the float32 rows x in place.  `uses_shared`: the tensor name of a shared
     part of the model (ModelSpec.shared) that attach() is handed once, after every part is bound."""
     uses_shared = None
+    takes_gated_add = False       # True: forward(x, ctx, pending=(results, logits)) first adds what ResidualGate.add would
 
     def attach(self, shared: "Shared"):
         pass

@@ -88,7 +88,9 @@ class LatentAttention(Mixer):
         w["o.weight"] = w["o.weight"].contiguous()
         self.position.to(uk.device)
 
-    def forward(self, xn, ctx, cache, out, reads_only=False):
+    can_store = True       # forward(store=True) writes the float32 rows `out` instead of adding into them
+
+    def forward(self, xn, ctx, cache, out, reads_only=False, store=False):
         if reads_only:
             raise ConfigError("latent_attention: the layer keeps a cache of its own")
         w = self.w
@@ -113,7 +115,10 @@ class LatentAttention(Mixer):
                                             warps=self.simt_warps, sinks=w.get("sink"), out_dim=rk)
         o = torch.empty((T, H * dv), dtype=a.dtype, device=a.device)
         ops.head_gemm(a, w["uv.weight"], o, a_head=rk, out_head=dv)
-        linear(o, w["o.weight"], out=out, accumulate=True)
+        if store:
+            linear(o, w["o.weight"], out=out, out_dtype=torch.float32)
+        else:
+            linear(o, w["o.weight"], out=out, accumulate=True)
         return out
 
     def weight_order(self):

@@ -26,10 +26,15 @@ class PolyNormFeedForward(FeedForward):
         self.w["up.weight"] = self.w["up.weight"].contiguous()
         self.w["down.weight"] = self.w["down.weight"].contiguous()
 
-    def forward(self, hn, ctx, out):
+    can_store = True       # forward(store=True) writes the float32 rows `out` instead of adding into them
+
+    def forward(self, hn, ctx, out, store=False):
         z = linear(hn, self.w["up.weight"], out_dtype=torch.float32)
         a = ops.poly_norm(z, self.w["act"], self.eps, hn.dtype)
-        linear(a, self.w["down.weight"], out=out, accumulate=True)
+        if store:
+            linear(a, self.w["down.weight"], out=out, out_dtype=torch.float32)
+        else:
+            linear(a, self.w["down.weight"], out=out, accumulate=True)
         return out
 
     def weight_order(self):

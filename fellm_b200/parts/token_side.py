@@ -5,7 +5,9 @@ slice of a table shared by all layers; a layer owns a slice),
 
 gelu_tanh(z) = 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))); the norm's weight is a plain vector.  One kernel per
 step and layer (ops.token_side), float32 sums.  The table belongs to a 'shared' part of the model ('table'), which
-this part asks for by its tensor's name."""
+this part asks for by its tensor's name.  A block whose
+sublayers reach the stream through gates hands their results and the gates' logits on to this part, whose kernel
+adds them on its way in (one launch less, and the stream is read once)."""
 from __future__ import annotations
 
 import torch
@@ -51,9 +53,11 @@ class TokenGatedSide(SideInput):
             table, wg, wp = table.float(), wg.float(), wp.float()
         self.table, self.w["gate.weight"], self.w["proj.weight"] = table, wg.contiguous(), wp.contiguous()
 
-    def forward(self, x, ctx):
+    takes_gated_add = True        # forward(pending=(results, logits)): the gated sublayers' sum is added in the same launch
+
+    def forward(self, x, ctx, pending=None):
         return ops.token_side(x, ctx.tokens, self.table, self.offset, self.w["gate.weight"], self.w["proj.weight"],
-                              self.w["norm.weight"], self.eps, status=ctx.status)
+                              self.w["norm.weight"], self.eps, status=ctx.status, pending=pending)
 
     def kernel_modules(self, dtype):
         return [("elementwise", None)]

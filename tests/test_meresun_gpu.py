@@ -303,6 +303,15 @@ def test_token_side_input_on_tensor_cores(T, d, m, layer, n_layers):
     got = ops.token_side(x.to(DEV).clone(), _i32(toks), W["side.embed"].bfloat16().to(DEV), layer * m, W["gate"].bfloat16().to(DEV),
                          W["proj"].bfloat16().to(DEV), W["norm"].float().to(DEV), 1e-6)
     assert (got.double().cpu() - want).abs().max() < 3e-2 * max(1.0, float(want.abs().max()))
+    # with the layer's gated results handed on: the same as adding them first
+    for n_sub in (1, 2):
+        ys = [torch.randn(T, d, generator=g).to(DEV) for _ in range(n_sub)]
+        zg = (torch.randn(T, 2 * d + 4, generator=g) * 3.0).to(DEV)
+        base = ops.gated_add(x.to(DEV).clone(), ys, zg)
+        want2 = base.double().cpu() + P.token_side_input(base.double().cpu(), toks, W, "", layer, m, 1e-6)
+        got2 = ops.token_side(x.to(DEV).clone(), _i32(toks), W["side.embed"].bfloat16().to(DEV), layer * m, W["gate"].bfloat16().to(DEV),
+                              W["proj"].bfloat16().to(DEV), W["norm"].float().to(DEV), 1e-6, pending=(ys, zg))
+        assert (got2.double().cpu() - want2).abs().max() < 3e-2 * max(1.0, float(want2.abs().max())), n_sub
 
 
 def test_a_sink_counts_once_and_unscaled():
