@@ -293,11 +293,61 @@ rmsnorm_groups_kernel(const float* __restrict__ x, const float* __restrict__ w, 
   for (int i = threadIdx.x; i < per; i += blockDim.x) o[i] = from_f<TO>((xr[i] * scale) * wg[i]);
 }
 
+// Parts of a multiple of 4 elements up to 2,048: a warp per (row, part), the part read once with 16-byte loads and
+// kept in registers between the sum and the scaling (a lane's share in order, then a butterfly: the same order whatever
+// else the step holds).
+template <typename TO, int VPL>
+__global__ void rmsnorm_groups_vec_kernel(const float* __restrict__ x, const float* __restrict__ w, TO* __restrict__ out,
+                                          const int* __restrict__ rows, int n_rows, int d, int groups, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (unit >= (long long)n_rows * groups) return;
+  const int orow = (int)(unit / groups), g = (int)(unit - (long long)orow * groups), per = d / groups;
+  const int irow = rows ? rows[orow] : orow;
+  const float4* xr = (const float4*)(x + (size_t)irow * d + (size_t)g * per);
+  const float4* wr = (const float4*)(w + (size_t)g * per);
+  const int nv = per >> 2;
+  float4 keep[VPL];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) {
+    const int i = lane + j * 32;
+    keep[j] = i < nv ? xr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+#pragma unroll
+  for (int j = 0; j < VPL; ++j)
+    ss = fmaf(keep[j].x, keep[j].x, fmaf(keep[j].y, keep[j].y, fmaf(keep[j].z, keep[j].z, fmaf(keep[j].w, keep[j].w, ss))));
+  ss = warp_sum(ss);
+  const float scale = 1.0f / sqrtf(ss / (float)per + eps);
+  TO* o = out + (size_t)orow * d + (size_t)g * per;
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) {
+    const int i = lane + j * 32;
+    if (i < nv) {
+      const float4 gw = wr[i];
+      store4(o + 4 * i, (keep[j].x * scale) * gw.x, (keep[j].y * scale) * gw.y, (keep[j].z * scale) * gw.z, (keep[j].w * scale) * gw.w);
+    }
+  }
+}
+
 FELLM_API int fellm_rmsnorm_groups(const float* x, const float* w, void* out, int out_is_bf16, const int* rows,
                                    int n_out_rows, int d, int groups, float eps, cudaStream_t stream) {
   if (n_out_rows <= 0) return 0;
   if (!x || !w || !out) return FELLM_ERR_ARG;
   if (groups < 1 || d % groups || groups > 65535) return FELLM_ERR_SIZE;
+  if ((d / groups) % 4 == 0 && d / groups <= 2048 && (((size_t)x | (size_t)w | (size_t)out) & 15) == 0) {
+    const int warps = 4, cls = launch_class_for_rows(n_out_rows, 0);
+    const long long units = (long long)n_out_rows * groups;
+    dim3 vgrid((unsigned)((units + warps - 1) / warps));
+#define GROUPS_VEC(TO_, VPL_) return launch_k_class(cls, rmsnorm_groups_vec_kernel<TO_, VPL_>, vgrid, dim3(warps * 32), 0, stream, 1, x, w, (TO_*)out, rows, n_out_rows, d, groups, eps)
+    if (d / groups <= 512) { if (out_is_bf16) GROUPS_VEC(bf16, 4); GROUPS_VEC(float, 4); }
+    if (d / groups <= 1024) { if (out_is_bf16) GROUPS_VEC(bf16, 8); GROUPS_VEC(float, 8); }
+    if (out_is_bf16) GROUPS_VEC(bf16, 16);
+    GROUPS_VEC(float, 16);
+#undef GROUPS_VEC
+  }
   const int per = d / groups, threads = per >= 1024 ? 256 : (per >= 256 ? 128 : 64);
   dim3 grid(n_out_rows, groups);
   if (out_is_bf16) return launch_k_class(launch_class_for_rows(n_out_rows, 0), rmsnorm_groups_kernel<bf16>, grid, dim3(threads), 0, stream, 1, x, w, (bf16*)out, rows, d, groups, eps);
@@ -330,10 +380,63 @@ poly_norm_kernel(const float* __restrict__ z, const float* __restrict__ coef, TO
   }
 }
 
+// Rows of a multiple of 4 elements up to 256 x 4 x KEEP: the row is read once, 16 bytes a lane, and stays in registers
+// between the three sums and the result (the sums: a thread's share in order, warps in order, as above).
+template <typename TO, int KEEP>
+__global__ void __launch_bounds__(256)
+poly_norm_vec_kernel(const float* __restrict__ z, const float* __restrict__ coef, TO* __restrict__ out, int F, float eps) {
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const float4* zr = (const float4*)(z + (size_t)blockIdx.x * F);
+  const int nv = F >> 2;
+  float4 keep[KEEP];
+#pragma unroll
+  for (int j = 0; j < KEEP; ++j) {
+    const int i = threadIdx.x + j * 256;
+    keep[j] = i < nv ? zr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  float s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+  for (int j = 0; j < KEEP; ++j) {
+    const float v[4] = {keep[j].x, keep[j].y, keep[j].z, keep[j].w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float v2 = v[e] * v[e], v3 = v2 * v[e];
+      s1 = fmaf(v[e], v[e], s1); s2 = fmaf(v2, v2, s2); s3 = fmaf(v3, v3, s3);
+    }
+  }
+  const float r1 = coef[0] / sqrtf(block_sum(s1, scratch) / (float)F + eps);
+  const float r2 = coef[1] / sqrtf(block_sum(s2, scratch) / (float)F + eps);
+  const float r3 = coef[2] / sqrtf(block_sum(s3, scratch) / (float)F + eps);
+  const float e0 = coef[3];
+  TO* o = out + (size_t)blockIdx.x * F;
+#pragma unroll
+  for (int j = 0; j < KEEP; ++j) {
+    const int i = threadIdx.x + j * 256;
+    if (i < nv) {
+      const float4 v = keep[j];
+      store4(o + 4 * i, fmaf(v.x, r1, fmaf(v.x * v.x, r2, fmaf(v.x * v.x * v.x, r3, e0))),
+             fmaf(v.y, r1, fmaf(v.y * v.y, r2, fmaf(v.y * v.y * v.y, r3, e0))),
+             fmaf(v.z, r1, fmaf(v.z * v.z, r2, fmaf(v.z * v.z * v.z, r3, e0))),
+             fmaf(v.w, r1, fmaf(v.w * v.w, r2, fmaf(v.w * v.w * v.w, r3, e0))));
+    }
+  }
+}
+
 FELLM_API int fellm_poly_norm(const float* z, const float* coef, void* out, int out_is_bf16, int rows, int F, float eps,
                               cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (!z || !coef || !out || F < 1) return FELLM_ERR_ARG;
+  if (F % 4 == 0 && F <= 256 * 4 * 16 && F >= 1024 && (((size_t)z | (size_t)out) & 15) == 0) {
+    const int cls = launch_class_for_rows(rows, 0);
+#define POLY_VEC(TO_, K_) return launch_k_class(cls, poly_norm_vec_kernel<TO_, K_>, dim3(rows), dim3(256), 0, stream, 1, z, coef, (TO_*)out, F, eps)
+    if (F <= 256 * 4 * 4) { if (out_is_bf16) POLY_VEC(bf16, 4); POLY_VEC(float, 4); }
+    if (F <= 256 * 4 * 8) { if (out_is_bf16) POLY_VEC(bf16, 8); POLY_VEC(float, 8); }
+    if (out_is_bf16) POLY_VEC(bf16, 16);
+    POLY_VEC(float, 16);
+#undef POLY_VEC
+  }
   const int threads = F >= 1024 ? 256 : 128;
   if (out_is_bf16) return launch_k_class(launch_class_for_rows(rows, 0), poly_norm_kernel<bf16>, dim3(rows), dim3(threads), 0, stream, 1, z, coef, (bf16*)out, F, eps);
   return launch_k_class(launch_class_for_rows(rows, 0), poly_norm_kernel<float>, dim3(rows), dim3(threads), 0, stream, 1, z, coef, (float*)out, F, eps);

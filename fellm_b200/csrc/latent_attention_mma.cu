@@ -309,7 +309,7 @@ static int launch_latent(const LatArgs& a, int n_items, int max_item_rows, int r
 FELLM_API int fellm_latent_attention_rk() { return RK; }
 FELLM_API int fellm_latent_attention_dr() { return DR; }
 // the key tile of a variant (0: portions, 1: single tokens): pages hold a multiple of it
-FELLM_API int fellm_latent_attention_key_tile(int variant) { return variant == 0 ? 32 : (RK % 64 == 0 ? 64 : 32); }
+FELLM_API int fellm_latent_attention_key_tile(int variant) { return variant != 1 ? 32 : (RK % 64 == 0 ? 64 : 32); }
 
 // variant 0: 64 rows a CTA (portions of prompts), n_splits must be 1; variant 1: 16 rows a CTA (single tokens),
 // n_splits >= 1 with scratch of rows * H * n_splits * (RK + 2) floats when above 1.
@@ -320,7 +320,7 @@ FELLM_API int fellm_latent_attention_mma(const void* q, const void* pool, const 
                                          const float* sinks, int variant, cudaStream_t stream) {
   if (n_items <= 0 || rows_total <= 0 || max_item_rows <= 0) return 0;
   if (!q || !pool || !block_table || !positions || !row_slot || !item_start || !out) return FELLM_ERR_ARG;
-  if (H < 1 || page_tokens < 1 || n_splits < 1 || n_splits > MAX_SPLITS || (n_splits > 1 && (!scratch || variant == 0))) return FELLM_ERR_ARG;
+  if (H < 1 || page_tokens < 1 || n_splits < 1 || n_splits > MAX_SPLITS || (n_splits > 1 && (!scratch || variant != 1))) return FELLM_ERR_ARG;
   LatArgs a;
   a.q = (const bf16*)q; a.pool = (const bf16*)pool; a.block_table = block_table; a.max_pages = max_pages;
   a.positions = positions; a.row_slot = row_slot; a.item_start = item_start; a.out = (bf16*)out; a.scratch = scratch;
