@@ -87,6 +87,8 @@ class LatentAttention(Mixer):
         w["uv.weight"] = w["uv.weight"].view(H, dv, rk).contiguous()
         w["o.weight"] = w["o.weight"].contiguous()
         self.position.to(uk.device)
+        if uk.is_cuda:
+            ops.latent_attention_reserve(uk.device)
 
     can_store = True       # forward(store=True) writes the float32 rows `out` instead of adding into them
 
@@ -101,10 +103,20 @@ class LatentAttention(Mixer):
                              xn.dtype, status=ctx.status)
         q = linear(cq, w["uq.weight"])
         T = q.shape[0]
+        on_mma = ops.latent_attention_takes(q, cache.pool, rk, dr, cache.page_tokens)
+        if on_mma and ops.latent_rotate_fusable(q, dn + dr, dn):
+            # the attention kernel rotates the queries' rotated parts itself, on their way into shared memory
+            qa = torch.empty((T, H * rk), dtype=q.dtype, device=q.device)
+            ops.head_gemm(q, w["ukT.weight"], qa, a_head=dn + dr, out_head=rk)
+            a = ops.latent_attention(qa, H, rk, dr, cache.pool, cache.block_table, ctx.positions, ctx.row_slot, ctx.item_start,
+                                     ctx.n_items, ctx.max_item_rows, ctx.max_len, cache.layer, cache.page_tokens, self.scale,
+                                     window=self.window, sinks=w.get("sink"),
+                                     q_rot=(q, dn + dr, dn, self.position.inv_freq, self.n_rot, self.magnitude))
+            return self._read_out(a, T, out, store)
         qa = torch.empty((T, H * (rk + dr)), dtype=q.dtype, device=q.device)
         ops.head_gemm(q, w["ukT.weight"], qa, a_head=dn + dr, out_head=rk + dr)
         ops.latent_rotate_q(q, H, dn, dr, qa, rk, self.position.inv_freq, self.n_rot, self.magnitude, ctx.positions)
-        if ops.latent_attention_takes(qa, cache.pool, rk, dr, cache.page_tokens):
+        if on_mma:
             a = ops.latent_attention(qa, H, rk, dr, cache.pool, cache.block_table, ctx.positions, ctx.row_slot, ctx.item_start,
                                      ctx.n_items, ctx.max_item_rows, ctx.max_len, cache.layer, cache.page_tokens, self.scale,
                                      window=self.window, sinks=w.get("sink"))
@@ -113,8 +125,13 @@ class LatentAttention(Mixer):
             a = ops.paged_attention_general(qa, H, rk + dr, 0, cache.pool, cache.block_table, ctx.positions, ctx.row_slot,
                                             cache.layer, cache.page_tokens, 1, self.scale, window=self.window,
                                             warps=self.simt_warps, sinks=w.get("sink"), out_dim=rk)
-        o = torch.empty((T, H * dv), dtype=a.dtype, device=a.device)
-        ops.head_gemm(a, w["uv.weight"], o, a_head=rk, out_head=dv)
+        return self._read_out(a, T, out, store)
+
+    def _read_out(self, a, T, out, store):
+        """The heads' values out of the latent's read-out, then W_o."""
+        w = self.w
+        o = torch.empty((T, self.H * self.dv), dtype=a.dtype, device=a.device)
+        ops.head_gemm(a, w["uv.weight"], o, a_head=self.rk, out_head=self.dv)
         if store:
             linear(o, w["o.weight"], out=out, out_dtype=torch.float32)
         else:

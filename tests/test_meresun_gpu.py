@@ -259,6 +259,27 @@ def test_latent_attention_on_tensor_cores(H, rk, dr, window, page, T):
         assert torch.isfinite(got).all(), items
         err = (got - want).abs().max()
         assert err < 2e-2 * max(1.0, float(want.abs().max())), (items, float(err))
+    if dr:
+        # the queries' rotated parts read from the query product's rows and rotated inside the kernel: the same as
+        # rotating them into place in front of it
+        dn, n_rot = 24, dr - 8 * (H % 2)                                    # (heads of 24 + dr; all or all but 8 elements rotated)
+        freq = (1.0 / (50.0 ** (torch.arange(n_rot // 2, dtype=torch.float32) / max(n_rot // 2, 1)))).to(DEV)
+        for items in ([(0, 3, 60), (1, 0, 9)], [(1, T - 1, 1), (0, 17, 1)]):
+            n_tok = sum(n for _, _, n in items)
+            pos = _i32([p for r, a, n in items for p in range(a, a + n)])
+            slot = _i32([r for r, a, n in items for _ in range(n)])
+            starts = _i32([0] + list(np.cumsum([n for _, _, n in items])))
+            qp = (torch.randn(n_tok, H * (dn + dr) + 8, generator=g) * 1.5).bfloat16().to(DEV)[:, :H * (dn + dr)]      # rows wider than the heads
+            qa = (torch.randn(n_tok, H, rk, generator=g) * 1.5).bfloat16().to(DEV)
+            full = torch.zeros(n_tok, H, D, dtype=torch.bfloat16, device=DEV)
+            full[:, :, :rk] = qa
+            full = full.view(n_tok, H * D)
+            ops.latent_rotate_q(qp, H, dn, dr, full, rk, freq, n_rot, 1.07, pos)
+            args = (pool, table, pos, slot, starts, len(items), max(n for _, _, n in items), max(a + n for _, a, n in items), 0, page, scale)
+            a = ops.latent_attention(full, H, rk, dr, *args, window=window, sinks=sinks).float()
+            b = ops.latent_attention(qa.view(n_tok, H * rk).contiguous(), H, rk, dr, *args, window=window, sinks=sinks,
+                                     q_rot=(qp, dn + dr, dn, freq, n_rot, 1.07)).float()
+            assert torch.isfinite(b).all() and (a - b).abs().max() < 1e-2 * max(1.0, float(a.abs().max())), items
     if window is not None and window > 1:
         # a window one position longer lets the key before the oldest in: the rows that point at it change
         i = window + 7 * ((T - 1 - window) // 7)
