@@ -15,7 +15,8 @@
 //   NG = 4, NC = 2   portions of prompts: 64 rows, key tiles of 32 through a two-stage cp.async ring
 //   NG = 1, NC = 4   single tokens (16 rows = the heads of a token), key tiles of 64; NC = 2 where RK / 4 is not a
 //                    multiple of 16.  The key range can be split over gridDim.z CTAs, which leave (m, l, sums) in a
-//                    scratch buffer; the CTA that finishes last for its rows puts them together.
+//                    scratch buffer that latent_merge_kernel puts together (a block a row: 8 x the parallelism of
+//                    a merge by the CTA that finishes last, which was tried and cost 40 us a layer).
 //
 // A key counts for the row of a token at position p iff p - window < key <= p (window 0: every key up to p).  A
 // sink per head joins the denominator once: exp(sink_h), not scaled, no value.  Rows of an item have consecutive
@@ -78,7 +79,6 @@ struct LatArgs {
   const int* positions; const int* row_slot; const int* item_start;
   bf16* out;                // [rows][H][RK]
   float* scratch;           // n_splits > 1: [rows * H][n_splits][RK + 2]
-  int* counters;            // n_splits > 1: one per CTA of a launch without the split, zero between launches
   const float* sinks;       // [H] or null
   int H, page_tokens, layer, layers_in_group, window, n_splits;
   float scale_log2;
@@ -278,33 +278,37 @@ __global__ void __launch_bounds__(NG * NC * 32, 1) latent_attention_kernel(LatAr
       if (Rg0 < n_rows) { r0[RK] = m0; r0[RK + 1] = l0; }
       if (Rg1 < n_rows) { r1[RK] = m1; r1[RK + 1] = l1; }
     }
-    // the CTA that finishes last for these rows puts the ranges together, in the order of the ranges:
-    // out = sum_s O_s 2^(m_s - m) / (sum_s l_s 2^(m_s - m) + 2^(sink - m)), m = max_s m_s; a warp a row
-    __shared__ int last;
-    __threadfence();
-    __syncthreads();
-    int* counter = a.counters + blockIdx.y * gridDim.x + blockIdx.x;
-    if (tid == 0) last = atomicAdd(counter, 1) == a.n_splits - 1;
-    __syncthreads();
-    if (!last) return;
-    __threadfence();
-    if (tid == 0) *counter = 0;                       // as the next launch expects it
-    for (int r = warp; r < rows_here; r += NTH / 32) {
-      const size_t row = (size_t)r_begin * H + R0 + r;
-      const float* base = a.scratch + row * a.n_splits * (RK + 2);
-      const float ms = lane < a.n_splits ? __ldcg(base + (size_t)lane * (RK + 2) + RK) : -INFINITY;
-      const float ls = lane < a.n_splits ? __ldcg(base + (size_t)lane * (RK + 2) + RK + 1) : 0.f;
-      const float m = warp_max(ms);
-      const float wgt = ms > -INFINITY ? exp2f(ms - m) : 0.f;
-      float L = warp_sum(ls * wgt);
-      if (a.sinks) L += exp2f(a.sinks[(R0 + r) % H] * LOG2E - m);
-      const float inv = 1.0f / L;
-      for (int e = lane; e < RK; e += 32) {
-        float acc = 0.f;
-        for (int sp = 0; sp < a.n_splits; ++sp) acc = fmaf(__ldcg(base + (size_t)sp * (RK + 2) + e), __shfl_sync(0xffffffffu, wgt, sp), acc);
-        a.out[row * RK + e] = __float2bfloat16_rn(acc * inv);
-      }
-    }
+  }
+}
+
+// The ranges of a split key walk put together, in the order of the ranges: out = sum_s O_s 2^(m_s - m) / (sum_s l_s
+// 2^(m_s - m) + 2^(sink - m)), m = max_s m_s.  A block per (token, head) row.
+__global__ void __launch_bounds__(128) latent_merge_kernel(const float* __restrict__ scratch, bf16* __restrict__ out,
+                                                           const float* __restrict__ sinks, int H, int n_splits) {
+  __shared__ float sm_m[MAX_SPLITS], sm_w[MAX_SPLITS];
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t row = blockIdx.x;
+  const float* base = scratch + row * n_splits * (RK + 2);
+  if (threadIdx.x < n_splits) {                    // every range's (m, l) at once
+    sm_m[threadIdx.x] = base[(size_t)threadIdx.x * (RK + 2) + RK];
+    sm_w[threadIdx.x] = base[(size_t)threadIdx.x * (RK + 2) + RK + 1];
+  }
+  __syncthreads();
+  float m = -INFINITY;
+  for (int s = 0; s < n_splits; ++s) m = fmaxf(m, sm_m[s]);
+  float L = 0.f;
+  for (int s = 0; s < n_splits; ++s) L += sm_m[s] > -INFINITY ? sm_w[s] * exp2f(sm_m[s] - m) : 0.f;
+  if (sinks) L += exp2f(sinks[row % H] * LOG2E - m);
+  const float inv = 1.0f / L;
+  __syncthreads();
+  if (threadIdx.x < n_splits) sm_w[threadIdx.x] = sm_m[threadIdx.x] > -INFINITY ? exp2f(sm_m[threadIdx.x] - m) : 0.f;
+  __syncthreads();
+  for (int e = threadIdx.x; e < RK; e += blockDim.x) {
+    float acc = 0.f;
+#pragma unroll 4
+    for (int s = 0; s < n_splits; ++s) acc = fmaf(base[(size_t)s * (RK + 2) + e], sm_w[s], acc);
+    out[row * RK + e] = __float2bfloat16_rn(acc * inv);
   }
 }
 
@@ -318,7 +322,10 @@ static int launch_latent(const LatArgs& a, int n_items, int max_item_rows, int r
   if (e != cudaSuccess) return (int)e;
   dim3 grid(ceil_div(max_item_rows * a.H, MQ), n_items, a.n_splits);
   const int cls = launch_class_for_rows(rows_total, 0);
-  return launch_k_class(cls, kern, grid, dim3(NG * NC * 32), smem, stream, 1, a);
+  int rc = launch_k_class(cls, kern, grid, dim3(NG * NC * 32), smem, stream, 1, a);
+  if (rc || a.n_splits == 1) return rc;
+  return launch_k_class(cls, latent_merge_kernel, dim3(rows_total * a.H), dim3(128), 0, stream, 1, (const float*)a.scratch, a.out,
+                        a.sinks, a.H, a.n_splits);
 }
 
 FELLM_API int fellm_latent_attention_rk() { return RK; }
@@ -328,22 +335,21 @@ FELLM_API int fellm_latent_attention_key_tile(int variant) { return variant != 1
 
 // variant 0: 64 rows a CTA (portions of prompts), n_splits must be 1; variant 1: 16 rows a CTA (single tokens),
 // qsrc (or null): the queries' rotated parts are read from there and rotated in the kernel, and q holds the RK
-// elements of a (token, head) row alone.  n_splits >= 1 (up to 32) with scratch of rows * H * n_splits * (RK + 2) floats and zeroed counters, one per CTA of
-// the launch without the split, when above 1.
+// elements of a (token, head) row alone.  n_splits >= 1 (up to 32) with scratch of rows * H * n_splits * (RK + 2) floats when above 1.
 FELLM_API int fellm_latent_attention_mma(const void* q, const void* pool, const int* block_table, int max_pages,
                                          const int* positions, const int* row_slot, const int* item_start, int n_items,
-                                         int max_item_rows, int rows_total, void* out, float* scratch, int* counters, int n_splits, int H,
+                                         int max_item_rows, int rows_total, void* out, float* scratch, int n_splits, int H,
                                          int page_tokens, int layer, int layers_in_group, float scale, int window,
                                          const float* sinks, int variant, const void* qsrc, int ldq, int q_head, int q_rot_off,
                                          const float* freq, int n_rot, float mag, cudaStream_t stream) {
   if (n_items <= 0 || rows_total <= 0 || max_item_rows <= 0) return 0;
   if (!q || !pool || !block_table || !positions || !row_slot || !item_start || !out) return FELLM_ERR_ARG;
-  if (H < 1 || page_tokens < 1 || n_splits < 1 || n_splits > MAX_SPLITS || (n_splits > 1 && (!scratch || !counters || variant != 1))) return FELLM_ERR_ARG;
+  if (H < 1 || page_tokens < 1 || n_splits < 1 || n_splits > MAX_SPLITS || (n_splits > 1 && (!scratch || variant != 1))) return FELLM_ERR_ARG;
   if (qsrc && ((ldq | q_head | q_rot_off) % 8 || ((size_t)qsrc & 15) || n_rot < 0 || n_rot > DR || (n_rot & 1) || (n_rot && !freq))) return FELLM_ERR_SIZE;
   LatArgs a;
   a.qsrc = DR ? (const bf16*)qsrc : nullptr; a.ldq = ldq; a.q_head = q_head; a.q_rot_off = q_rot_off; a.n_rot = n_rot; a.freq = freq; a.mag = mag;
   a.q = (const bf16*)q; a.pool = (const bf16*)pool; a.block_table = block_table; a.max_pages = max_pages;
-  a.positions = positions; a.row_slot = row_slot; a.item_start = item_start; a.out = (bf16*)out; a.scratch = scratch; a.counters = counters;
+  a.positions = positions; a.row_slot = row_slot; a.item_start = item_start; a.out = (bf16*)out; a.scratch = scratch;
   a.sinks = sinks; a.H = H; a.page_tokens = page_tokens; a.layer = layer; a.layers_in_group = layers_in_group;
   a.window = window > 0 ? window : 0; a.n_splits = n_splits; a.scale_log2 = scale * LOG2E;
   if (variant == 0) return launch_latent<4, 2>(a, n_items, max_item_rows, rows_total, stream);

@@ -993,7 +993,6 @@ def latent_rotate_q(q, H, dn, dr, q_abs, rk, freq, n_rot, mag, positions):
 LATENT_ATTENTION_MMA = os.environ.get("FELLM_B200_LATENT_ATTENTION_MMA", "1") != "0"
 LATENT_SINGLE_ROWS = 32        # up to this many (token, head) rows an item: the kernel's form for single tokens
 LATENT_MAX_SPLITS = 16
-_latent_counters = {}
 
 
 def latent_attention_takes(q_abs, pool, rk: int, dr: int, page_tokens: int) -> bool:
@@ -1006,14 +1005,6 @@ def latent_attention_takes(q_abs, pool, rk: int, dr: int, page_tokens: int) -> b
 def latent_rotate_fusable(q, q_head: int, off: int) -> bool:
     """Whether latent_attention can read the queries' rotated parts from q itself (16-byte chunks)."""
     return q.dtype == torch.bfloat16 and q.stride(1) == 1 and q.stride(0) % 8 == 0 and q_head % 8 == 0 and off % 8 == 0 and q.data_ptr() % 16 == 0
-
-
-def latent_attention_reserve(device):
-    """The counters of split key walks (zero between launches): made before any step is captured."""
-    device = torch.device(device)
-    if device not in _latent_counters:
-        _latent_counters[device] = torch.zeros(1 << 16, dtype=torch.int32, device=device)
-    return _latent_counters[device]
 
 
 def latent_attention_modules(rk: int, dr: int):
@@ -1048,7 +1039,7 @@ def latent_attention(q_abs, H, rk, dr, pool, block_table, positions, row_slot, i
     if out is None:
         out = torch.empty((T, H * rk), dtype=torch.bfloat16, device=q_abs.device)
     variant = 1 if max_item_rows * H <= LATENT_SINGLE_ROWS else 0
-    n_splits, scratch, counters = 1, None, None
+    n_splits, scratch = 1, None
     if variant == 1:
         # few CTAs walk many keys: split the walk so that the SMs have work (a constant of the step's shape)
         kt = 64 if rk % 64 == 0 else 32
@@ -1059,14 +1050,11 @@ def latent_attention(q_abs, H, rk, dr, pool, block_table, positions, row_slot, i
         n_splits = max(1, min(tiles // 2, 148 // max(ctas, 1), LATENT_MAX_SPLITS))
         if n_splits > 1:
             scratch = torch.empty((T * H * n_splits * (rk + 2),), dtype=torch.float32, device=q_abs.device)
-            counters = latent_attention_reserve(q_abs.device)      # zero between launches: the CTA that merges a split puts its counter back
-            if ctas > counters.numel():
-                n_splits, scratch, counters = 1, None, None
     f = _fn("latent_attention_mma", "fellm_latent_attention_mma",
-            [_c_p, _c_p, _c_p, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int,
+            [_c_p, _c_p, _c_p, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int,
              _c_int, _c_f, _c_int, _c_p, _c_int, _c_p, _c_int, _c_int, _c_int, _c_p, _c_int, _c_f, _c_p], defines={"LAT_RK": rk, "LAT_DR": dr})
     _check(f(_p(q_abs), _p(pool), _p(block_table), block_table.shape[1], _p(positions), _p(row_slot), _p(item_start),
-             int(n_items), int(max_item_rows), T, _p(out), _p(scratch), _p(counters), n_splits, H, page_tokens, layer, pool.shape[1],
+             int(n_items), int(max_item_rows), T, _p(out), _p(scratch), n_splits, H, page_tokens, layer, pool.shape[1],
              float(scale), int(window or 0), _p(sinks), variant, _p(qsrc), ldq, int(q_head), int(q_off), _p(freq), int(n_rot), float(mag),
              _stream()), "latent_attention")
     return out

@@ -87,8 +87,6 @@ class LatentAttention(Mixer):
         w["uv.weight"] = w["uv.weight"].view(H, dv, rk).contiguous()
         w["o.weight"] = w["o.weight"].contiguous()
         self.position.to(uk.device)
-        if uk.is_cuda:
-            ops.latent_attention_reserve(uk.device)
 
     can_store = True       # forward(store=True) writes the float32 rows `out` instead of adding into them
 
@@ -104,8 +102,9 @@ class LatentAttention(Mixer):
         q = linear(cq, w["uq.weight"])
         T = q.shape[0]
         on_mma = ops.latent_attention_takes(q, cache.pool, rk, dr, cache.page_tokens)
-        if on_mma and ops.latent_rotate_fusable(q, dn + dr, dn):
-            # the attention kernel rotates the queries' rotated parts itself, on their way into shared memory
+        if on_mma and ctx.max_item_rows * H <= ops.LATENT_SINGLE_ROWS and ops.latent_rotate_fusable(q, dn + dr, dn):
+            # single tokens: the attention kernel rotates the queries' rotated parts itself, on their way into shared
+            # memory (a launch less; for portions the rotation in front is cheaper than the kernel's longer start)
             qa = torch.empty((T, H * rk), dtype=q.dtype, device=q.device)
             ops.head_gemm(q, w["ukT.weight"], qa, a_head=dn + dr, out_head=rk)
             a = ops.latent_attention(qa, H, rk, dr, cache.pool, cache.block_table, ctx.positions, ctx.row_slot, ctx.item_start,
