@@ -81,7 +81,7 @@ def test_gated_sum_of_the_sublayers():
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("T,d,m,layer,n_layers", [(1, 96, 5, 1, 3), (7, 72, 1, 0, 2), (30, 256, 16, 3, 4), (3, 1024, 64, 2, 3)])
+@pytest.mark.parametrize("T,d,m,layer,n_layers", [(1, 96, 5, 1, 3), (7, 72, 1, 0, 2), (30, 320, 16, 3, 4), (3, 1024, 64, 2, 3)])
 def test_token_side_input(dtype, T, d, m, layer, n_layers):
     """The layer's own part of the table (the parts beside it hold numbers a thousand times larger), gated by the stream,
     projected, over its root mean square, times the norm's weight, added to the stream."""
@@ -102,7 +102,7 @@ def test_token_side_input(dtype, T, d, m, layer, n_layers):
     assert (got.double().cpu() - want).abs().max() < (1e-4 if dtype == torch.float32 else 3e-2 * max(1.0, float(want.abs().max())))
 
 
-@pytest.mark.parametrize("n,base,scaling", [(8, 100.0, (4.0, 64, 8.0, 1.0)), (32, 500000.0, (8.0, 1024, 32.0, 1.0)), (6, 10.0, (2.0, 1.0, 1.0, 1.0)),
+@pytest.mark.parametrize("n,base,scaling", [(8, 100.0, (4.0, 64, 8.0, 1.0)), (32, 250000.0, (6.0, 2048, 24.0, 1.0)), (6, 10.0, (2.0, 1.0, 1.0, 1.0)),
                                             (16, 10000.0, None), (64, 1e6, (40.0, 4096, 32.0, 1.0)), (2, 50.0, (3.0, 16, 4.0, 0.5))])
 def test_scaled_frequencies_of_the_position_part(n, base, scaling):
     from fellm_b200.parts.base import build_part
@@ -401,7 +401,7 @@ def test_a_far_key_among_hundreds(dtype, window, page):
         assert float(plain_row(T - 1).abs().max()) > 5 * float(torch.stack([plain_row(i) for i in range(T - 8, T - 4)]).abs().max())
 
 
-@pytest.mark.parametrize("E,top,groups", [(6, 2, (3, 2)), (12, 4, (2, 1)), (4, 2, (4, 2)), (8, 3, None), (6, 3, (2, 2)), (2, 2, (1, 1)),
+@pytest.mark.parametrize("E,top,groups", [(6, 2, (3, 2)), (12, 3, (2, 1)), (4, 2, (4, 2)), (8, 3, None), (6, 3, (2, 2)), (2, 2, (1, 1)),
                                           (9, 2, (3, 1)), (16, 8, (4, 3))])
 def test_router_choice_in_groups(E, top, groups):
     """Sigmoid scores, the correction in the choice and not in the weights, groups ranked by their two best choice
