@@ -356,14 +356,14 @@ FELLM_API int fellm_rmsnorm_groups(const float* x, const float* w, void* out, in
 
 // ---------------------------------------------------------------- polynomial activation over unit powers
 // out = a N(z) + b N(z^2) + c N(z^3) + e, powers element by element, N(v) = v / sqrt(mean(v^2) + eps) over the row;
-// coef = (a, b, c, e) on the device.  z float32 [T, F] (the product's sums as they are), out in the activation dtype.
+// coef = (a, b, c, e) on the device.  z float32 [T, F] (the product's sums as they are; rows ldz apart), out in the activation dtype.
 template <typename TO>
 __global__ void __launch_bounds__(256)
-poly_norm_kernel(const float* __restrict__ z, const float* __restrict__ coef, TO* __restrict__ out, int F, float eps) {
+poly_norm_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ coef, TO* __restrict__ out, int F, float eps) {
   __shared__ float scratch[33];
   pdl_launch_dependents();
   pdl_wait();
-  const float* zr = z + (size_t)blockIdx.x * F;
+  const float* zr = z + (size_t)blockIdx.x * ldz;
   float s1 = 0.f, s2 = 0.f, s3 = 0.f;
   for (int i = threadIdx.x; i < F; i += blockDim.x) {
     const float v = zr[i], v2 = v * v, v3 = v2 * v;
@@ -384,11 +384,11 @@ poly_norm_kernel(const float* __restrict__ z, const float* __restrict__ coef, TO
 // between the three sums and the result (the sums: a thread's share in order, warps in order, as above).
 template <typename TO, int KEEP>
 __global__ void __launch_bounds__(256)
-poly_norm_vec_kernel(const float* __restrict__ z, const float* __restrict__ coef, TO* __restrict__ out, int F, float eps) {
+poly_norm_vec_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ coef, TO* __restrict__ out, int F, float eps) {
   __shared__ float scratch[33];
   pdl_launch_dependents();
   pdl_wait();
-  const float4* zr = (const float4*)(z + (size_t)blockIdx.x * F);
+  const float4* zr = (const float4*)(z + (size_t)blockIdx.x * ldz);
   const int nv = F >> 2;
   float4 keep[KEEP];
 #pragma unroll
@@ -424,13 +424,13 @@ poly_norm_vec_kernel(const float* __restrict__ z, const float* __restrict__ coef
   }
 }
 
-FELLM_API int fellm_poly_norm(const float* z, const float* coef, void* out, int out_is_bf16, int rows, int F, float eps,
+FELLM_API int fellm_poly_norm(const float* z, int ldz, const float* coef, void* out, int out_is_bf16, int rows, int F, float eps,
                               cudaStream_t stream) {
   if (rows <= 0) return 0;
-  if (!z || !coef || !out || F < 1) return FELLM_ERR_ARG;
-  if (F % 4 == 0 && F <= 256 * 4 * 16 && F >= 1024 && (((size_t)z | (size_t)out) & 15) == 0) {
+  if (!z || !coef || !out || F < 1 || ldz < F) return FELLM_ERR_ARG;
+  if (F % 4 == 0 && ldz % 4 == 0 && F <= 256 * 4 * 16 && F >= 1024 && (((size_t)z | (size_t)out) & 15) == 0) {
     const int cls = launch_class_for_rows(rows, 0);
-#define POLY_VEC(TO_, K_) return launch_k_class(cls, poly_norm_vec_kernel<TO_, K_>, dim3(rows), dim3(256), 0, stream, 1, z, coef, (TO_*)out, F, eps)
+#define POLY_VEC(TO_, K_) return launch_k_class(cls, poly_norm_vec_kernel<TO_, K_>, dim3(rows), dim3(256), 0, stream, 1, z, ldz, coef, (TO_*)out, F, eps)
     if (F <= 256 * 4 * 4) { if (out_is_bf16) POLY_VEC(bf16, 4); POLY_VEC(float, 4); }
     if (F <= 256 * 4 * 8) { if (out_is_bf16) POLY_VEC(bf16, 8); POLY_VEC(float, 8); }
     if (out_is_bf16) POLY_VEC(bf16, 16);
@@ -438,8 +438,8 @@ FELLM_API int fellm_poly_norm(const float* z, const float* coef, void* out, int 
 #undef POLY_VEC
   }
   const int threads = F >= 1024 ? 256 : 128;
-  if (out_is_bf16) return launch_k_class(launch_class_for_rows(rows, 0), poly_norm_kernel<bf16>, dim3(rows), dim3(threads), 0, stream, 1, z, coef, (bf16*)out, F, eps);
-  return launch_k_class(launch_class_for_rows(rows, 0), poly_norm_kernel<float>, dim3(rows), dim3(threads), 0, stream, 1, z, coef, (float*)out, F, eps);
+  if (out_is_bf16) return launch_k_class(launch_class_for_rows(rows, 0), poly_norm_kernel<bf16>, dim3(rows), dim3(threads), 0, stream, 1, z, ldz, coef, (bf16*)out, F, eps);
+  return launch_k_class(launch_class_for_rows(rows, 0), poly_norm_kernel<float>, dim3(rows), dim3(threads), 0, stream, 1, z, ldz, coef, (float*)out, F, eps);
 }
 
 // ---------------------------------------------------------------- sublayers through sigmoid gates into the stream

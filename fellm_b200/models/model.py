@@ -15,7 +15,7 @@ import torch
 from .. import ops
 from ..config.errors import ConfigError
 from ..parts.base import ParamDecl, build_part
-from ..parts.linear import LazyNorm
+from ..parts.linear import LazyNorm, linear
 from ..parts.spec import ModelSpec
 
 
@@ -80,20 +80,30 @@ def _parallel_gated(block, x, ctx, cache, act_dtype, reads_only):
     if block.gate is None:
         raise ConfigError("the 'parallel_gated' arrangement needs the layer's gates")
     h = block.norm1.forward(x, act_dtype)
-    zg = block.gate.logits(h)
+    pre = {}
+    if block.joint is not None:
+        # everything that reads h through float32 sums (the gates' logits, the mixer's down projections, a dense
+        # feed-forward's up product) is ONE product; each part gets its columns
+        w, bias, cols = block.joint
+        z = linear(h, w, bias, out_dtype=torch.float32)
+        pre = {key: {"pre": z[:, a:b]} for key, (a, b) in cols.items()}
+    zg = pre["gate"]["pre"] if "gate" in pre else block.gate.logits(h)
     # (a sublayer that says `can_store` writes its result instead of adding it: no rows of zeros to make)
     if getattr(block.mixer, "can_store", False):
-        results = [block.mixer.forward(h, ctx, cache, torch.empty_like(x), reads_only=reads_only, store=True)]
+        results = [block.mixer.forward(h, ctx, cache, torch.empty_like(x), reads_only=reads_only, store=True, **pre.get("mixer", {}))]
     else:
-        results = [block.mixer.forward(h, ctx, cache, torch.zeros_like(x), reads_only=reads_only)]
+        results = [block.mixer.forward(h, ctx, cache, torch.zeros_like(x), reads_only=reads_only, **pre.get("mixer", {}))]
     if block.ffn is not None:
         if getattr(block.ffn, "can_store", False):
-            results.append(block.ffn.forward(h, ctx, torch.empty_like(x), store=True))
+            results.append(block.ffn.forward(h, ctx, torch.empty_like(x), store=True, **pre.get("ffn", {})))
         else:
-            results.append(block.ffn.forward(h, ctx, torch.zeros_like(x)))
+            results.append(block.ffn.forward(h, ctx, torch.zeros_like(x), **pre.get("ffn", {})))
     if getattr(block.side, "takes_gated_add", False):
         return results, zg          # the side input's kernel reads the stream anyway: it adds the gated results on its way in
     block.gate.add(x, results, zg)
+
+
+_parallel_gated.joins_inputs = True
 
 
 def _with_children(part):
@@ -116,6 +126,33 @@ class Block:
         self.gate = build_part("gate", spec.gate, dtype) if spec.gate is not None else None
         self.side = build_part("side", spec.side, dtype) if spec.side is not None else None
         self.norm_after = None
+        self.joint = None           # (weight [N, d], bias float32 [N], {"gate" | "mixer" | "ffn": (first column, end)}) after join_inputs()
+
+    def join_inputs(self):
+        """After every part is bound: the rows of the parts that read the block's input through a product with
+        float32 sums (a part names them `input_rows`) become ONE matrix, of which each part keeps a view; a part's bias
+        (`input_bias`) lies at its rows of the joint bias, zeros elsewhere.  Only where the arrangement makes that
+        product (`joins_inputs`), all rows have one dtype and at least two parts take part (a part whose rows are not a
+        multiple of 8 stays out: the parts' columns start on 32 bytes)."""
+        if not getattr(self.arrange, "joins_inputs", False):
+            return
+        users = [(key, p) for key, p in (("mixer", self.mixer), ("gate", self.gate), ("ffn", self.ffn))
+                 if p is not None and getattr(p, "input_rows", None) and p.input_rows in p.w and p.w[p.input_rows].shape[0] % 8 == 0]
+        mats = [p.w[p.input_rows] for _, p in users]
+        if len(users) < 2 or any(m.dtype != mats[0].dtype or m.shape[1] != mats[0].shape[1] for m in mats):
+            return
+        joint = torch.cat(mats, 0).contiguous()
+        bias = torch.zeros(joint.shape[0], dtype=torch.float32, device=joint.device)
+        cols, at = {}, 0
+        for (key, p), m in zip(users, mats):
+            n = m.shape[0]
+            p.w[p.input_rows] = joint[at:at + n]
+            name = getattr(p, "input_bias", None)
+            if name and name in p.w:
+                bias[at:at + n] = p.w[name]
+            cols[key] = (at, at + n)
+            at += n
+        self.joint = (joint, bias, cols)
 
     def parts(self):
         return [q for p in (self.norm1, self.mixer, self.norm2, self.ffn, self.gate, self.side) if p is not None
@@ -191,6 +228,8 @@ class Model:
                 if want not in by_name:
                     raise ConfigError(f"a part asks for the shared tensor {want!r}, which the model does not have")
                 part.attach(by_name[want])
+        for block in self.blocks:
+            block.join_inputs()
 
     def kernel_modules(self):
         mods = []

@@ -202,15 +202,15 @@ def rmsnorm_groups(x, w, eps: float, groups: int, out_dtype, rows=None, out=None
 
 
 def poly_norm(z, coef, eps: float, out_dtype, out=None):
-    """z float32 [T, F], coef float32 [4] = (a, b, c, e) -> a N(z) + b N(z^2) + c N(z^3) + e in out_dtype, powers
+    """z float32 [T, F] (columns of a wider matrix are fine), coef float32 [4] = (a, b, c, e) -> a N(z) + b N(z^2) + c N(z^3) + e in out_dtype, powers
     element by element, N = over the row's root mean square (eps under the root)."""
     _dev(z, coef)
-    assert z.dtype == torch.float32 and z.is_contiguous() and coef.dtype == torch.float32 and coef.numel() == 4
+    assert z.dtype == torch.float32 and z.stride(1) == 1 and coef.dtype == torch.float32 and coef.numel() == 4
     T, F = z.shape
     if out is None:
         out = torch.empty((T, F), dtype=out_dtype, device=z.device)
-    f = _fn("elementwise", "fellm_poly_norm", [_c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_f, _c_p])
-    _check(f(_p(z), _p(coef), _p(out), _is_bf16(out), T, F, float(eps), _stream()), "poly_norm")
+    f = _fn("elementwise", "fellm_poly_norm", [_c_p, _c_int, _c_p, _c_p, _c_int, _c_int, _c_int, _c_f, _c_p])
+    _check(f(_p(z), max(z.stride(0), F), _p(coef), _p(out), _is_bf16(out), T, F, float(eps), _stream()), "poly_norm")
     return out
 
 

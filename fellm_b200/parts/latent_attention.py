@@ -89,13 +89,14 @@ class LatentAttention(Mixer):
         self.position.to(uk.device)
 
     can_store = True       # forward(store=True) writes the float32 rows `out` instead of adding into them
+    input_rows = "down.weight"      # forward(pre=z): the float32 product of the layer's input with these rows, made elsewhere
 
-    def forward(self, xn, ctx, cache, out, reads_only=False, store=False):
+    def forward(self, xn, ctx, cache, out, reads_only=False, store=False, pre=None):
         if reads_only:
             raise ConfigError("latent_attention: the layer keeps a cache of its own")
         w = self.w
         H, dn, dr, dv, rq, rk = self.H, self.dn, self.dr, self.dv, self.rq, self.rk
-        z = linear(xn, w["down.weight"], out_dtype=torch.float32)
+        z = pre if pre is not None else linear(xn, w["down.weight"], out_dtype=torch.float32)
         cq = ops.latent_prep(z, self.q_off, rq, self.c_off, rk, self.r_off, dr, w["dq.norm"], w["dkv.norm"], self.eps,
                              self.position.inv_freq, self.n_rot, self.magnitude, ctx.positions, ctx.row_slot, cache,
                              xn.dtype, status=ctx.status)

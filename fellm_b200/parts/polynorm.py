@@ -28,8 +28,10 @@ class PolyNormFeedForward(FeedForward):
 
     can_store = True       # forward(store=True) writes the float32 rows `out` instead of adding into them
 
-    def forward(self, hn, ctx, out, store=False):
-        z = linear(hn, self.w["up.weight"], out_dtype=torch.float32)
+    input_rows = "up.weight"        # forward(pre=z): the float32 product of the layer's input with these rows, made elsewhere
+
+    def forward(self, hn, ctx, out, store=False, pre=None):
+        z = pre if pre is not None else linear(hn, self.w["up.weight"], out_dtype=torch.float32)
         a = ops.poly_norm(z, self.w["act"], self.eps, hn.dtype)
         if store:
             linear(a, self.w["down.weight"], out=out, out_dtype=torch.float32)

@@ -31,6 +31,8 @@ class SigmoidGates(ResidualGate):
         self.w["weight"] = torch.cat([m.to(dt) for m in mats], 0).contiguous()           # [n size, size]
         self.w["bias"] = torch.cat([self.w.pop(f"{s}.bias") for s in range(self.n)]).contiguous()
 
+    input_rows, input_bias = "weight", "bias"       # the block may make the logits in a product it shares with its sublayers
+
     def logits(self, h):
         """h [T, size] -> float32 [T, n size]: sublayer s's logits at columns [s size, (s + 1) size)."""
         return linear(h, self.w["weight"], self.w["bias"], out_dtype=torch.float32)
