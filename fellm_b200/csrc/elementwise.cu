@@ -546,8 +546,8 @@ __device__ __forceinline__ void ts_mma16816(float* d, const unsigned* a, unsigne
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-template <int NT>
-__global__ void __launch_bounds__(256)
+template <int NT, int W>
+__global__ void __launch_bounds__(32 * W)
 token_side_mma_kernel(float* __restrict__ x, const float* __restrict__ y0, const float* __restrict__ y1,
                       const float* __restrict__ zg, int ldz, const int* __restrict__ tokens, const bf16* __restrict__ table,
                       int ldt, int off, int vocab, const bf16* __restrict__ Wg, const bf16* __restrict__ Wp,
@@ -559,15 +559,15 @@ token_side_mma_kernel(float* __restrict__ x, const float* __restrict__ y0, const
   constexpr int LDP = 72;
   bf16* Xs = (bf16*)ts_smem;                               // [16][d + 8]
   bf16* Gs = Xs + 16 * ldx;                                // [16][m + 8]
-  float* part = (float*)(Gs + 16 * ldg);                   // [8 warps][16 rows][64 + 8]: the warps' shares of a gate product
-  float* red = part + 8 * 16 * LDP;                        // [8 warps][16 rows]
-  int* toks = (int*)(red + 128);                           // [16]
+  float* part = (float*)(Gs + 16 * ldg);                   // [W warps][16 rows][64 + 8]: the warps' shares of a gate product
+  float* red = part + W * 16 * LDP;                        // [W warps][16 rows]
+  int* toks = (int*)(red + W * 16);                        // [16]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
   const int row0 = blockIdx.x * 16;
   // the rows of x, with what the layer's gated sublayers add taken in on the way (y0 != null): x is written back
   // with it, and every product below reads the sum
 #pragma unroll 4
-  for (int i = tid; i < 16 * (d / 4); i += 256) {
+  for (int i = tid; i < 16 * (d / 4); i += 32 * W) {
     const int r = i / (d / 4), k = 4 * (i - r * (d / 4));
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
     if (row0 + r < T) {
@@ -602,7 +602,7 @@ token_side_mma_kernel(float* __restrict__ x, const float* __restrict__ y0, const
     float z[8][4];
 #pragma unroll
     for (int n = 0; n < 8; ++n) z[n][0] = z[n][1] = z[n][2] = z[n][3] = 0.f;
-    for (int ks = warp; ks < d / 16; ks += 8) {
+    for (int ks = warp; ks < d / 16; ks += W) {
       unsigned b[8][2];
 #pragma unroll
       for (int n = 0; n < 8; ++n) {
@@ -620,12 +620,12 @@ token_side_mma_kernel(float* __restrict__ x, const float* __restrict__ y0, const
       *(float2*)(part + (warp * 16 + g + 8) * LDP + 8 * n + 2 * c) = make_float2(z[n][2], z[n][3]);
     }
     __syncthreads();
-    for (int i = tid; i < 16 * 64; i += 256) {
+    for (int i = tid; i < 16 * 64; i += 32 * W) {
       const int r = i >> 6, cl = i & 63;
       if (cl < ntc * 8) {
         float sum = 0.f;
 #pragma unroll
-        for (int ww = 0; ww < 8; ++ww) sum += part[(ww * 16 + r) * LDP + cl];
+        for (int ww = 0; ww < W; ++ww) sum += part[(ww * 16 + r) * LDP + cl];
         const int tok = toks[r];
         const float e = tok >= 0 ? to_f(table[(size_t)tok * ldt + off + nc0 + cl]) : 0.f;
         Gs[r * ldg + nc0 + cl] = __float2bfloat16_rn(gelu_tanh_f(sum) * e);
@@ -633,11 +633,12 @@ token_side_mma_kernel(float* __restrict__ x, const float* __restrict__ y0, const
     }
     __syncthreads();
   }
-  // y = g W_proj^T: this warp's columns [warp d / 8, (warp + 1) d / 8), n_tiles tiles of 8 (tiles beyond them repeat the last)
-  const int n_tiles = d / 64, col0 = warp * (d / 8);
+  // y = g W_proj^T: this warp's columns [warp d / W, (warp + 1) d / W), n_tiles tiles of 8 (tiles beyond them repeat the last)
+  const int n_tiles = d / (8 * W), col0 = warp * (d / W);
   float acc[NT][4];
 #pragma unroll
   for (int n = 0; n < NT; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+#pragma unroll 2
   for (int ks = 0; ks < m / 16; ++ks) {
     unsigned b[NT][2];
 #pragma unroll
@@ -664,7 +665,7 @@ token_side_mma_kernel(float* __restrict__ x, const float* __restrict__ y0, const
   __syncthreads();
   float t0 = 0.f, t1 = 0.f;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) { t0 += red[i * 16 + g]; t1 += red[i * 16 + g + 8]; }
+  for (int i = 0; i < W; ++i) { t0 += red[i * 16 + g]; t1 += red[i * 16 + g + 8]; }
   const float sc0 = 1.0f / sqrtf(t0 / (float)d + eps), sc1 = 1.0f / sqrtf(t1 / (float)d + eps);
   // (the loads of a few tiles first, then their sums and stores: the loads are in flight together)
   constexpr int NB = NT < 4 ? NT : 4;
@@ -692,20 +693,22 @@ token_side_mma_kernel(float* __restrict__ x, const float* __restrict__ y0, const
   }
 }
 
-template <int NT>
+template <int NT, int W>
 static int launch_token_side_mma(float* x, const float* y0, const float* y1, const float* zg, int ldz, const int* tokens,
                                  const bf16* table, int ldt, int off, int vocab, const bf16* Wg, const bf16* Wp, const float* w,
                                  int rows, int d, int m, float eps, int* status, cudaStream_t stream) {
-  const size_t smem = (size_t)16 * (d + 8) * 2 + (size_t)16 * (m + 8) * 2 + (8 * 16 * 72 + 128) * sizeof(float) + 16 * sizeof(int);
-  auto kern = token_side_mma_kernel<NT>;
+  const size_t smem = (size_t)16 * (d + 8) * 2 + (size_t)16 * (m + 8) * 2 + (W * 16 * 72 + W * 16) * sizeof(float) + 16 * sizeof(int);
+  auto kern = token_side_mma_kernel<NT, W>;
   if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  return launch_k_class(launch_class_for_rows(rows, 0), kern, dim3((rows + 15) / 16), dim3(256), smem, stream, 1, x, y0, y1, zg, ldz,
+  return launch_k_class(launch_class_for_rows(rows, 0), kern, dim3((rows + 15) / 16), dim3(32 * W), smem, stream, 1, x, y0, y1, zg, ldz,
                         tokens, table, ldt, off, vocab, Wg, Wp, w, rows, d, m, eps, status);
 }
 
 // bfloat16 tables; d a multiple of 64 up to 2048, m a multiple of 16 up to 512, tables that start on 4 bytes.
 // y0 (and y1) float32 [rows, d] with zg float32 [rows, >= d (2 d)]: x += y0 sigmoid(zg[:, :d]) (+ y1 sigmoid(zg[:, d:2d]))
 // first, in the same launch (what gated_add does), and the side input is computed from that sum.
+// Up to 16 rows (one block, a decode step): 16 warps where d is a multiple of 128, which halves the block's chains
+// (the order of a row's sums then differs from the 8-warp form's: rounding).
 FELLM_API int fellm_token_side_mma(float* x, const float* y0, const float* y1, const float* zg, int ldz, const int* tokens,
                                    const void* table, int ldt, int off, int vocab, const void* Wg, const void* Wp, const float* w,
                                    int rows, int d, int m, float eps, int* status, cudaStream_t stream) {
@@ -713,13 +716,20 @@ FELLM_API int fellm_token_side_mma(float* x, const float* y0, const float* y1, c
   if (!x || !tokens || !table || !Wg || !Wp || !w || (y0 && !zg) || (y1 && !y0)) return FELLM_ERR_ARG;
   if (d < 64 || d % 64 || d > 2048 || m < 16 || m % 16 || m > 512) return FELLM_ERR_SIZE;
   if ((((size_t)Wg | (size_t)Wp) & 3) || (((size_t)x | (size_t)y0 | (size_t)y1 | (size_t)zg) & 15) || ((size_t)w & 7) || (y0 && (ldz & 3))) return FELLM_ERR_ARG;
+#define TS_LAUNCH(N_, W_) return launch_token_side_mma<N_, W_>(x, y0, y1, zg, ldz, tokens, (const bf16*)table, ldt, off, vocab, (const bf16*)Wg, (const bf16*)Wp, w, rows, d, m, eps, status, stream)
+  if (rows <= 16 && d % 128 == 0) {
+    const int nt = d / 128;
+    if (nt <= 2) TS_LAUNCH(2, 16);
+    if (nt <= 4) TS_LAUNCH(4, 16);
+    if (nt <= 8) TS_LAUNCH(8, 16);
+    TS_LAUNCH(16, 16);
+  }
   const int nt = d / 64;
-#define TS_LAUNCH(N_) return launch_token_side_mma<N_>(x, y0, y1, zg, ldz, tokens, (const bf16*)table, ldt, off, vocab, (const bf16*)Wg, (const bf16*)Wp, w, rows, d, m, eps, status, stream)
-  if (nt <= 2) TS_LAUNCH(2);
-  if (nt <= 4) TS_LAUNCH(4);
-  if (nt <= 8) TS_LAUNCH(8);
-  if (nt <= 16) TS_LAUNCH(16);
-  TS_LAUNCH(32);
+  if (nt <= 2) TS_LAUNCH(2, 8);
+  if (nt <= 4) TS_LAUNCH(4, 8);
+  if (nt <= 8) TS_LAUNCH(8, 8);
+  if (nt <= 16) TS_LAUNCH(16, 8);
+  TS_LAUNCH(32, 8);
 #undef TS_LAUNCH
 }
 

@@ -306,10 +306,11 @@ def test_head_products_on_tensor_cores(T, H, N, K, a_head, out_head):
     assert (out.double().cpu() - want).abs().max() < 2e-2 * float(want.abs().max())
 
 
-@pytest.mark.parametrize("T,d,m,layer,n_layers", [(1, 64, 16, 1, 3), (37, 128, 32, 0, 2), (300, 1024, 64, 2, 3), (16, 2048, 48, 1, 2), (17, 192, 16, 0, 1)])
+@pytest.mark.parametrize("T,d,m,layer,n_layers", [(1, 64, 16, 1, 3), (37, 128, 32, 0, 2), (300, 1024, 64, 2, 3), (16, 2048, 48, 1, 2), (17, 192, 16, 0, 1), (9, 1024, 64, 0, 2), (3, 384, 80, 1, 2)])
 def test_token_side_input_on_tensor_cores(T, d, m, layer, n_layers):
-    """The side input's kernel for bfloat16 tables (16 rows a block): a last block that is not full, rows whose x
-    differ by orders of magnitude, the layer's own part of the table."""
+    """The side input's kernel for bfloat16 tables (16 rows a block; 16 warps instead of 8 for a single block of a
+    width that is a multiple of 128): a last block that is not full, rows whose x differ by orders of magnitude, the
+    layer's own part of the table."""
     from fellm_b200 import ops
     g = torch.Generator().manual_seed(d + m)
     vocab = 37
