@@ -15,20 +15,6 @@
 // Norms, angles and the rotation are float32 in both engines.
 #include "common.cuh"
 
-__device__ __forceinline__ float block_sum_lt(float v, float* scratch /* [33] */) {
-  v = warp_sum(v);
-  __syncthreads();
-  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    float t = 0.f;
-    for (int i = 0; i < (int)(blockDim.x >> 5); ++i) t += scratch[i];
-    scratch[32] = t;
-  }
-  __syncthreads();
-  return scratch[32];
-}
-
 // (u, v) at pair i of a row at position pos
 __device__ __forceinline__ void rotate_pair(float& u, float& v, int pos, float f, float mag) {
   float sn, cs;
@@ -46,22 +32,31 @@ latent_prep_kernel(const float* __restrict__ z, int ldz, int q_off, int rq, int 
                    const int* __restrict__ positions, const int* __restrict__ row_slot,
                    const int* __restrict__ block_table, int max_pages, TC* __restrict__ pool, int page_tokens, int layer,
                    int layers_in_group, TO* __restrict__ cq, int* __restrict__ status) {
-  __shared__ float scratch[33];
+  __shared__ float scratch[68];
   pdl_launch_dependents();
   pdl_wait();
   const int row = blockIdx.x;
   const float* zr = z + (size_t)row * ldz;
-  // the query latent
-  float ss = 0.f;
-  for (int i = threadIdx.x; i < rq; i += blockDim.x) { const float v = zr[q_off + i]; ss = fmaf(v, v, ss); }
-  const float sq = 1.0f / sqrtf(block_sum_lt(ss, scratch) / (float)rq + eps);
-  for (int i = threadIdx.x; i < rq; i += blockDim.x) cq[(size_t)row * rq + i] = from_f<TO>((zr[q_off + i] * sq) * wq[i]);
-  // the key-value latent and the rotated key part into the token's cache row
-  ss = 0.f;
-  for (int i = threadIdx.x; i < rk; i += blockDim.x) { const float v = zr[c_off + i]; ss = fmaf(v, v, ss); }
-  const float sc = 1.0f / sqrtf(block_sum_lt(ss, scratch) / (float)rk + eps);
+  // (the page's number is asked for first: its two dependent loads run under the sums)
   const int pos = positions[row];
   const int page = block_table[(size_t)row_slot[row] * max_pages + pos / page_tokens];
+  // both latents' sums of squares in one reduction: a thread's share in order, the warps in order
+  float sq_ = 0.f, sc_ = 0.f;
+  for (int i = threadIdx.x; i < rq; i += blockDim.x) { const float v = zr[q_off + i]; sq_ = fmaf(v, v, sq_); }
+  for (int i = threadIdx.x; i < rk; i += blockDim.x) { const float v = zr[c_off + i]; sc_ = fmaf(v, v, sc_); }
+  sq_ = warp_sum(sq_); sc_ = warp_sum(sc_);
+  if ((threadIdx.x & 31) == 0) { scratch[threadIdx.x >> 5] = sq_; scratch[32 + (threadIdx.x >> 5)] = sc_; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float a = 0.f, b = 0.f;
+    for (int i = 0; i < (int)(blockDim.x >> 5); ++i) { a += scratch[i]; b += scratch[32 + i]; }
+    scratch[64] = a; scratch[65] = b;
+  }
+  __syncthreads();
+  const float sq = 1.0f / sqrtf(scratch[64] / (float)rq + eps), sc = 1.0f / sqrtf(scratch[65] / (float)rk + eps);
+  // the query latent
+  for (int i = threadIdx.x; i < rq; i += blockDim.x) cq[(size_t)row * rq + i] = from_f<TO>((zr[q_off + i] * sq) * wq[i]);
+  // the key-value latent and the rotated key part into the token's cache row
   if (page < 0) {
     if (threadIdx.x == 0 && status) atomicExch(status, 2);
     return;
