@@ -102,6 +102,33 @@ def test_tensor_names_and_shapes():
     assert shape("l0.mlp.router") == (6, 96) and shape("l0.mlp.correction") == (6,) and shape("l0.mlp.e1.down") == (96, 40)
 
 
+def test_one_product_for_everything_that_reads_a_layer_input():
+    """After binding, the mixer's down projections, the gates and a dense up of a layer are views of ONE matrix, in
+    that order, each part's columns recorded; the gates' bias lies at their rows of the joint bias, zeros elsewhere; a
+    layer without a dense feed-forward joins two parts."""
+    from fellm_b200.weights.loader import bind_tensors
+    from fellm_b200.weights.random_init import random_tensors
+    _, _, spec = _spec(U.CFG_A)
+    model = build_model(spec, "float32")
+    tensors = random_tensors(model, 3)
+    bind_tensors(model, tensors, "cpu")
+    for i, block in enumerate(model.blocks):
+        w, bias, cols = block.joint
+        parts = {"mixer": block.mixer, "gate": block.gate, "ffn": block.ffn}
+        assert list(cols) == (["mixer", "gate", "ffn"] if i == 1 else ["mixer", "gate"])         # layer 1 is the dense one
+        end = 0
+        for key, (a, b) in cols.items():
+            part = parts[key]
+            view = part.w[part.input_rows]
+            assert a == end and view.shape[0] == b - a and view.data_ptr() == w[a:b].data_ptr() and torch.equal(view, w[a:b])
+            end = b
+        assert end == w.shape[0] == bias.numel()
+        a, b = cols["gate"]
+        assert torch.equal(bias[a:b], block.gate.w["bias"]) and float(bias[:a].abs().sum()) == 0.0 and float(bias[b:].abs().sum()) == 0.0
+        assert torch.equal(block.gate.w["weight"][:96].float(), tensors[f"l{i}.rg1"].float())
+    assert torch.equal(model.blocks[1].ffn.w["up.weight"].float(), tensors["l1.mlp.up"].float())
+
+
 def test_cache_needs_and_window_trimming():
     _, _, spec = _spec(U.CFG_A)
     needs = build_model(spec, "float32").cache_needs()
