@@ -93,7 +93,17 @@ CFG_W = config(256, 1024, [
     layer(mixer(8, 128, 64, 128, 512, 192, 4096, 0.07), moe(512, 8, 2, (4, 2), limit=0.5)),
 ], groups=2, side=16)
 
-CONFIGS = {"A": (CFG_A, 31), "B": (CFG_B, 32), "C": (CFG_C, 33), "D": (CFG_D, 34), "W": (CFG_W, 35)}
+# M: small, and of the sizes the tensor-core kernels of the bfloat16 engine take (latents of a multiple of 32, cache rows
+# of a multiple of 16, a width of a multiple of 128, a side input of 16), run with pages of 64: windows longer and
+# shorter than a page, a layer without a rotated part's scaling, a loop of two passes over the first two layers
+CFG_M = config(180, 128, [
+    layer(mixer(5, 24, 16, 16, 40, 64, 70, 0.2, 10000.0, (4.0, 64, 8.0, 1.0)), dense(96)),
+    layer(mixer(3, 16, 32, 24, 24, 32, 33, 0.25), moe(24, 4, 2, (2, 1), limit=0.3)),
+    layer(mixer(2, 32, 16, 40, 32, 96, 200, 0.15, 500000.0, (8.0, 256, 32.0, 1.0))),
+], loop=(0, 2, 2), groups=2, emb=1.5, side=16)
+
+CONFIGS = {"A": (CFG_A, 31), "B": (CFG_B, 32), "C": (CFG_C, 33), "D": (CFG_D, 34), "W": (CFG_W, 35), "M": (CFG_M, 36)}
+PAGE_TOKENS = {"M": 64}          # (the other small configurations run with pages of 16)
 _tmp = tempfile.TemporaryDirectory(prefix="fellm_b200_meresun_")
 
 # random weights as the framework's random mode makes them, then some scaled so that no mechanism hides behind small
@@ -157,8 +167,8 @@ def make_engine(name_or_folder: str, dtype: str, **opts):
     from fellm_b200.config.options import EngineOptions
     from fellm_b200.engine import Engine
     folder = model_folder(name_or_folder) if name_or_folder in CONFIGS else name_or_folder
-    o = dict(dtype=dtype, n_ctx=1024, ctx_past_model=True, max_requests=4, max_tokens=2048, page_tokens=16,
-             cuda_graphs=False, n_batch=2048)
+    o = dict(dtype=dtype, n_ctx=1024, ctx_past_model=True, max_requests=4, max_tokens=2048,
+             page_tokens=PAGE_TOKENS.get(name_or_folder, 16), cuda_graphs=False, n_batch=2048)
     o.update(opts)
     return Engine.open(folder, EngineOptions(**o))
 

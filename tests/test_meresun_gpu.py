@@ -517,7 +517,7 @@ def engines(request):
     made.clear()
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "M"])
 def test_whole_prompt(engines, name):
     T = 150
     got = U.run_cuts(engines(name), "a", U.tokens(name, T, 0), [T])
@@ -553,7 +553,7 @@ def test_layers_one_by_one(engines, name):
         assert float(err.max() if engines.dtype == "float32" else torch.quantile(err, 0.9)) < tol, (i, float(err.max()))
 
 
-@pytest.mark.parametrize("name", ["A", "B", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "D", "M"])
 def test_prompt_against_token_by_token(engines, name):
     T = 90
     eng = engines(name)
@@ -565,7 +565,8 @@ def test_prompt_against_token_by_token(engines, name):
 
 
 @pytest.mark.parametrize("name,cuts", [("A", [2, 2, 3, 17, 2, 21, 1, 1, 23, 2, 48]), ("B", [7, 2, 71, 2, 9, 64, 3]),
-                                       ("C", [15, 2, 1, 16, 17, 2, 33]), ("D", [8, 2, 9, 1, 10, 65])])
+                                       ("C", [15, 2, 1, 16, 17, 2, 33]), ("D", [8, 2, 9, 1, 10, 65]), ("M", [31, 2, 30, 1, 2, 63, 2, 7]),
+                                       ("M", [64, 2, 69])])
 def test_portions_of_many_sizes(engines, name, cuts):
     T = 170
     eng = engines(name)
@@ -574,12 +575,12 @@ def test_portions_of_many_sizes(engines, name, cuts):
     U.assert_close(got, U.plain_logits(name, T, 3), engines.dtype)
 
 
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "M"])
 def test_unequal_batch_against_each_alone_with_slots_and_pages_that_come_again(engines, name):
     """Four requests of different lengths share steps (portions beside single tokens), end at different times and
     are followed by new ones in the slots and pages they gave back; the pool holds less than all of them together."""
     from fellm_b200.engine import StepItem
-    eng = engines(name, max_tokens=448)
+    eng = engines(name, max_tokens=640 if name == "M" else 448)          # (M's pages hold 64 tokens: ten of them)
     lengths = [97, 5, 140, 33, 61, 120, 2, 75]
     plans = {i: (U.tokens(name, n, 10 + i), [3, 1, 2, 40, 1, 1, 17, 2, 64][i % 3:]) for i, n in enumerate(lengths)}
     waiting, live, got = list(plans), {}, {i: [] for i in plans}
