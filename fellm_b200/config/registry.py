@@ -74,4 +74,4 @@ def config_from_dict(d: dict):
 
 def _load_builtin():
     # importing the module registers it
-    from ..models import lfm2, meresun, robazen, samusun  # noqa: F401
+    from ..models import lfm2, meresun, nalizen, robazen, samusun  # noqa: F401

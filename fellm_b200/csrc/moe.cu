@@ -167,7 +167,7 @@ template <typename TA, typename TW>
 __global__ void __launch_bounds__(ROUTER_WARPS * 32)
 moe_router_kernel(const TA* __restrict__ h, int ldh, const TW* __restrict__ Wr, int K, int E, int top, int renorm,
                   int* __restrict__ idx, float* __restrict__ w, int sigmoid, const float* __restrict__ corr,
-                  int n_groups, int keep, int gtop) {
+                  int n_groups, int keep, int gtop, const float* __restrict__ bias) {
   extern __shared__ float zs[];                 // [E]; the sigmoid form: + [E + n_groups]
   const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const TA* hr = h + (size_t)t * ldh;
@@ -176,7 +176,7 @@ moe_router_kernel(const TA* __restrict__ h, int ldh, const TW* __restrict__ Wr, 
     float s = 0.f;
     for (int k = lane; k < K; k += 32) s = fmaf(to_f(hr[k]), to_f(wr[k]), s);
     s = warp_sum(s);
-    if (lane == 0) zs[e] = s;
+    if (lane == 0) zs[e] = bias ? s + bias[e] : s;
   }
   __syncthreads();
   if (warp == 0) {
@@ -187,7 +187,8 @@ moe_router_kernel(const TA* __restrict__ h, int ldh, const TW* __restrict__ Wr, 
 
 FELLM_API int fellm_moe_router(const void* h, int h_bf16, int ldh, const void* Wr, int w_bf16, int T, int K, int E, int top,
                                int renorm, int* idx, float* w, int sigmoid, const float* corr, int n_groups, int keep,
-                               int gtop, cudaStream_t stream) {
+                               int gtop, const float* bias, cudaStream_t stream) {
+  // bias (float32 [E] or null) is added to the logits before anything looks at them.
   // sigmoid = 0: softmax scores over all experts.  sigmoid = 1: sigmoid scores, a correction added for the choice
   // (corr float32 [E] or null), the choice limited to `keep` of n_groups groups ranked by their gtop best choice scores.
   if (T <= 0) return 0;
@@ -196,7 +197,7 @@ FELLM_API int fellm_moe_router(const void* h, int h_bf16, int ldh, const void* W
   if (sigmoid && (E % n_groups || keep < 1 || keep > n_groups || gtop < 1 || top > (E / n_groups) * keep)) return FELLM_ERR_SIZE;
   if (!h || !Wr || !idx || !w) return FELLM_ERR_ARG;
   const size_t sh = (size_t)(sigmoid ? 2 * E + n_groups : E) * sizeof(float);
-#define ROUTER(TA_, TW_) moe_router_kernel<TA_, TW_><<<T, ROUTER_WARPS * 32, sh, stream>>>((const TA_*)h, ldh, (const TW_*)Wr, K, E, top, renorm, idx, w, sigmoid, corr, n_groups, keep, gtop)
+#define ROUTER(TA_, TW_) moe_router_kernel<TA_, TW_><<<T, ROUTER_WARPS * 32, sh, stream>>>((const TA_*)h, ldh, (const TW_*)Wr, K, E, top, renorm, idx, w, sigmoid, corr, n_groups, keep, gtop, bias)
   if (h_bf16) { if (w_bf16) ROUTER(bf16, bf16); else ROUTER(bf16, float); }
   else { if (w_bf16) ROUTER(float, bf16); else ROUTER(float, float); }
 #undef ROUTER

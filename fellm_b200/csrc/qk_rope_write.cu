@@ -236,3 +236,82 @@ FELLM_API int fellm_qk_rope_write(const void* qkv, int act_bf16, const float* q_
                   (const float*)qkv, q_w, k_w, eps, inv_freq, pairing, positions, row_slot, block_table, max_pages,
                   (float*)pool, layer, layers_in_group, page_tokens, (float*)q_out, T, H, G, hd, rot_dim, write_kv, status);
 }
+
+// ---------------------------------------------------------------- rotation and unit norm in place
+// For layers whose keys and values differ in size (or that read another layer's pages): the heads of q (n_q at column
+// 0 of a row) and of k (n_k at column k_off) are rotated on their first rot_dim elements and then, unit_norm, divided
+// by their root mean square over hd (no weight), where they lie; the cache write and the attention read them from
+// there.  A warp a (row, head); a head's values stay in registers between the sum and the scaling, so a bfloat16 value
+// is rounded once.  hd <= 512.
+#define RN_MAXP 8      // pairs a lane: rot_dim <= 512
+#define RN_MAXT 16     // unrotated elements a lane
+template <typename TA>
+__global__ void __launch_bounds__(128)
+qk_rotate_norm_kernel(TA* __restrict__ qkv, int ld, int T, int n_q, int n_k, int k_off, int hd, int rot_dim,
+                      const float* __restrict__ inv_freq, int pairing, const int* __restrict__ positions, float eps,
+                      int unit_norm) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  const int heads = n_q + n_k;
+  if (warp >= T * heads) return;
+  const int row = warp / heads, head = warp - row * heads;
+  TA* p = qkv + (size_t)row * ld + (head < n_q ? (size_t)head * hd : (size_t)k_off + (size_t)(head - n_q) * hd);
+  const float pos = (float)positions[row];
+  const int half = rot_dim >> 1;
+  float ra[RN_MAXP], rb[RN_MAXP], tl[RN_MAXT];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < RN_MAXP; ++j) {
+    const int i = lane + 32 * j;
+    ra[j] = rb[j] = 0.f;
+    if (i < half) {
+      const int ia = pairing ? i : 2 * i, ib = pairing ? i + half : 2 * i + 1;
+      float sn, cs;
+      sincosf(pos * inv_freq[i], &sn, &cs);
+      const float a = to_f(p[ia]), b = to_f(p[ib]);
+      ra[j] = a * cs - b * sn; rb[j] = b * cs + a * sn;
+      ss = fmaf(ra[j], ra[j], fmaf(rb[j], rb[j], ss));
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < RN_MAXT; ++j) {
+    const int i = rot_dim + lane + 32 * j;
+    tl[j] = 0.f;
+    if (i < hd) { tl[j] = to_f(p[i]); ss = fmaf(tl[j], tl[j], ss); }
+  }
+  float scale = 1.0f;
+  if (unit_norm) scale = 1.0f / sqrtf(warp_sum(ss) / (float)hd + eps);
+#pragma unroll
+  for (int j = 0; j < RN_MAXP; ++j) {
+    const int i = lane + 32 * j;
+    if (i < half) {
+      const int ia = pairing ? i : 2 * i, ib = pairing ? i + half : 2 * i + 1;
+      p[ia] = from_f<TA>(ra[j] * scale); p[ib] = from_f<TA>(rb[j] * scale);
+    }
+  }
+  if (unit_norm) {
+#pragma unroll
+    for (int j = 0; j < RN_MAXT; ++j) {
+      const int i = rot_dim + lane + 32 * j;
+      if (i < hd) p[i] = from_f<TA>(tl[j] * scale);
+    }
+  }
+}
+
+FELLM_API int fellm_qk_rotate_norm(void* qkv, int is_bf16, int ld, int T, int n_q, int n_k, int k_off, int hd, int rot_dim,
+                                   const float* inv_freq, int pairing, const int* positions, float eps, int unit_norm,
+                                   cudaStream_t stream) {
+  if (T <= 0 || n_q + n_k <= 0) return 0;
+  if (!inv_freq) rot_dim = 0;
+  if (hd < 1 || hd > 32 * RN_MAXT || rot_dim < 0 || rot_dim > hd || (rot_dim & 1) || rot_dim > 64 * RN_MAXP) return FELLM_ERR_SIZE;
+  if (!qkv || !positions || n_q < 0 || n_k < 0) return FELLM_ERR_ARG;
+  if (!rot_dim && !unit_norm) return 0;
+  const long long warps = (long long)T * (n_q + n_k);
+  dim3 grid((unsigned)((warps + 3) / 4));
+  const int cls = launch_class_for_rows(T, 2);
+  if (is_bf16) return launch_k_class(cls, qk_rotate_norm_kernel<bf16>, grid, dim3(128), 0, stream, 1, (bf16*)qkv, ld, T, n_q, n_k, k_off, hd,
+                                     rot_dim, inv_freq, pairing, positions, eps, unit_norm);
+  return launch_k_class(cls, qk_rotate_norm_kernel<float>, grid, dim3(128), 0, stream, 1, (float*)qkv, ld, T, n_q, n_k, k_off, hd,
+                        rot_dim, inv_freq, pairing, positions, eps, unit_norm);
+}

@@ -6,6 +6,8 @@
 //   delta_scan         gated delta rule:  S = g S; u = beta (v - S^T k); S += k u^T; o = S^T q
 //   decay_bonus_scan   o = (S + diag(u) k v^T)^T r; S = diag(w) S + k v^T   (per-channel decay, bonus for the current token)
 //   retention_scan     S = decay_h S + k v^T; o = S^T q, q and k rotated by position
+//   gated_write_scan   S = diag(f) S + (1 - f) v^T; o = S^T q: the forget gate also weighs what is written
+//   token_shift        h + (h_prev - h) * mu from float32 rows into the activation dtype
 //   head_norm_gate     per head: o / rms(o) * weight * act(gate)
 //   branch_combine     x += mean over branches of rms_unit(branch) * weight
 //
@@ -105,11 +107,11 @@ FELLM_API int fellm_causal_conv_act(const void* x, int is_bf16, int ldx, const f
 // ---------------------------------------------------------------- token shift
 // out[s][t][c] = h[t][c] + (h[t-1][c] - h[t][c]) * mu[s][c]; the row before a portion is the slot's state, which
 // then takes the portion's last row.  Same grid as the convolution; row tile 0 reads the slot and then writes it.
-template <typename TA>
+template <typename TA, typename TO = TA>
 __global__ void token_shift_mix_kernel(const TA* __restrict__ h, const float* __restrict__ mu, int n_mix,
                                        float* __restrict__ state, long long slot_stride,
                                        const int* __restrict__ item_start, const int* __restrict__ item_slot,
-                                       TA* __restrict__ out, int T, int d) {
+                                       TO* __restrict__ out, int T, int d) {
   const int item = blockIdx.y;
   const int c = blockIdx.x * CH_TILE + threadIdx.x;
   if (c >= d) return;
@@ -125,7 +127,7 @@ __global__ void token_shift_mix_kernel(const TA* __restrict__ h, const float* __
     float prev = r > 0 ? to_f(h[(size_t)(r0 + r - 1) * d + c]) : first_prev;
     float diff = prev - cur;
     for (int s = 0; s < n_mix; ++s)
-      out[((size_t)s * T + r0 + r) * d + c] = from_f<TA>(fmaf(diff, mu[(size_t)s * d + c], cur));
+      out[((size_t)s * T + r0 + r) * d + c] = from_f<TO>(fmaf(diff, mu[(size_t)s * d + c], cur));
   }
   if (owner) st[c] = to_f(h[(size_t)(r0 + n - 1) * d + c]);
 }
@@ -143,6 +145,22 @@ FELLM_API int fellm_token_shift_mix(const void* h, int is_bf16, const float* mu,
   else
     token_shift_mix_kernel<float><<<grid, block, 0, stream>>>((const float*)h, mu, n_mix, state, slot_stride, item_start,
                                                               item_slot, (float*)out, T, d);
+  return launch_status();
+}
+
+// The same from float32 rows (a residual stream that a sublayer reads as it is) into the activation dtype: the slot keeps
+// the float32 row, the mix is rounded once.
+FELLM_API int fellm_token_shift(const float* h, const float* mu, float* state, long long slot_stride, const int* item_start,
+                                const int* item_slot, void* out, int out_is_bf16, int T, int n_items, int d, int max_item_rows,
+                                cudaStream_t stream) {
+  if (n_items <= 0 || d <= 0) return 0;
+  if (!h || !mu || !state || !item_start || !item_slot || !out) return FELLM_ERR_ARG;
+  if (max_item_rows < 1) max_item_rows = 1;
+  dim3 grid(ceil_div(d, CH_TILE), n_items, ceil_div(max_item_rows, ROW_TILE)), block(CH_TILE, max_item_rows == 1 ? 1 : 8);
+  if (out_is_bf16)
+    token_shift_mix_kernel<float, bf16><<<grid, block, 0, stream>>>(h, mu, 1, state, slot_stride, item_start, item_slot, (bf16*)out, T, d);
+  else
+    token_shift_mix_kernel<float, float><<<grid, block, 0, stream>>>(h, mu, 1, state, slot_stride, item_start, item_slot, (float*)out, T, d);
   return launch_status();
 }
 
@@ -216,6 +234,8 @@ FELLM_API int fellm_lowrank_expand(const float* z, int ldz, const void* W2, int 
 //   delta rule (k^ = k / |k|, q^ = q / |q| / sqrt(dk), decay g per head or per channel):
 //       A = g k^,  B = g q^,  G = g,  K = k^,  c = k^ . q^      (S^T q after the write = g S^T q + u (k.q))
 //   decay and bonus:  B = r,  G = w,  K = k,  c = sum_i r_i u_i k_i,  A unused
+//   gated write (q = SiLU(q raw), f = l + (1 - l) sigmoid(f raw + bias), l a lower bound per channel):
+//       B = f q,  G = f,  K = 1 - f,  c = sum_i (1 - f_i) q_i      (S^T q after the write = S^T (f q) + v c)
 // so the chain from token to token is one reduction and one multiply-add per element.  Eight producer warps stage
 // these vectors for the next tokens (loads, unit norms, decays, sigmoids) in shared memory while four consumer
 // warps run the chain over the tokens staged before: one block barrier per stage.  KS is chosen from the model's
@@ -241,6 +261,8 @@ struct ScanArgs {
   // retention: the rows' positions, the rotary frequencies [rot / 2], how many leading elements of a head are rotated,
   // the decay of each head, and what the rotated keys are multiplied by
   const int* pos; const float* inv_freq; int rot; const float* decay_h; float kscale;
+  // gated write: the forget gate's lower bound and its bias, [H, dk] each
+  const float* lower; const float* fbias;
 };
 
 template <int VE> __device__ __forceinline__ void load_vec(const float* p, float* out) {
@@ -271,7 +293,7 @@ __device__ __forceinline__ void scan_stage(const ScanArgs& a, float* buf, int DK
   const int g = MODE == 2 ? h : h / (a.H / a.G);
   const TA* x0p = (const TA*)a.q + (size_t)g * dk;                                         // q, or r
   const TA* x1p = MODE == 2 ? (const TA*)a.k + (size_t)h * dk : x0p + a.k_off;             // k
-  const float* x2p = (MODE == 0 || MODE == 3) ? nullptr : a.gch + (size_t)h * dk;           // the decay per channel
+  const float* x2p = (MODE == 0 || MODE >= 3) ? nullptr : a.gch + (size_t)h * dk;           // the decay per channel
   // The values of this block's columns and the tokens' logits are asked for first and stored last: their latency
   // runs under the vectors' loads.
   constexpr int VMAX = (SC_MAX_TOK * 32 * SC_CONSUMERS + PT - 1) / PT;
@@ -372,6 +394,28 @@ __device__ __forceinline__ void scan_stage(const ScanArgs& a, float* buf, int DK
     for (int u = 0; u < TPW; ++u) {
       const int t = pw + u * SC_PRODUCERS;
       if (t < n_tok && lane == 0) { cc[t] = c[u]; beta[t] = 1.f; }
+    }
+  } else if (MODE == 4) {
+    // gated write: everything of the gate in float32; rows behind dk keep K = 0, so the state's padding stays zero
+    const float* lo = a.lower + (size_t)h * dk; const float* fb = a.fbias + (size_t)h * dk;
+#pragma unroll
+    for (int u = 0; u < TPW; ++u) {
+      const int t = pw + u * SC_PRODUCERS;
+      if (t >= n_tok) continue;
+      float* Bt = B + t * DKP; float* Gt = Gd + t * DKP; float* Kt = KK + t * DKP;
+      float c = 0.f;
+      for (int i = lane; i < DKP; i += 32) {
+        float fq = 0.f, f = 0.f, w = 0.f;
+        if (i < dk) {
+          const float q = silu_f(Bt[i]), l = lo[i];
+          f = fmaf(1.0f - l, sigmoid_f(Kt[i] + fb[i]), l);
+          w = 1.0f - f; fq = f * q;
+          c = fmaf(w, q, c);
+        }
+        Bt[i] = fq; Gt[i] = f; Kt[i] = w;
+      }
+      c = warp_sum(c);
+      if (lane == 0) { cc[t] = c; beta[t] = 1.f; }
     }
   } else if (MODE == 3) {
     // retention: rotate the leading `rot` elements of q and k (element i with i + rot/2, angle = position * frequency i),
@@ -646,6 +690,22 @@ FELLM_API int fellm_retention_scan(const void* qkv, int is_bf16, int ld, int k_o
   a.item_start = item_start; a.item_slot = item_slot; a.out = out; a.H = H; a.G = H; a.dk = dk; a.dv = dv;
   a.pos = positions; a.inv_freq = inv_freq; a.rot = rot; a.decay_h = decay; a.kscale = kscale;
   return is_bf16 ? scan_launch<3, bf16>(a, n_items, max_item_rows, stream) : scan_launch<3, float>(a, n_items, max_item_rows, stream);
+}
+
+// Gated write: S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T, o_t = S_t^T q_t with q = SiLU(q raw) and
+// f = lower + (1 - lower) sigmoid(f raw + bias).  z float32 [T, ld]: q raw at column 0 (H x dk), f raw at f_off (H x dk),
+// v at v_off (H x dv), as their product left them; lower, bias float32 [H * dk].
+FELLM_API int fellm_gated_write_scan(const float* z, int ld, int f_off, int v_off, const float* lower, const float* bias,
+                                     float* state, long long slot_stride, const int* item_start, const int* item_slot,
+                                     float* out, int n_items, int H, int dk, int dv, int max_item_rows, cudaStream_t stream) {
+  if (n_items <= 0) return 0;
+  if (dk < 1 || dk > 1024 || dv < 1 || H < 1) return FELLM_ERR_SIZE;
+  if (!z || !lower || !bias || !state || !item_start || !item_slot || !out) return FELLM_ERR_ARG;
+  ScanArgs a = {};
+  a.q = z; a.ld = ld; a.k_off = f_off; a.v_off = v_off; a.state = state; a.slot_stride = slot_stride;
+  a.item_start = item_start; a.item_slot = item_slot; a.out = out; a.H = H; a.G = H; a.dk = dk; a.dv = dv;
+  a.lower = lower; a.fbias = bias;
+  return scan_launch<4, float>(a, n_items, max_item_rows, stream);
 }
 
 // ---------------------------------------------------------------- per-head norm and gate

@@ -106,6 +106,32 @@ def _parallel_gated(block, x, ctx, cache, act_dtype, reads_only):
 _parallel_gated.joins_inputs = True
 
 
+@register_arrangement("outnorm")
+def _outnorm(block, x, ctx, cache, act_dtype, reads_only):
+    """x += norm1(mixer(x)); x += norm2(ffn(x)): the sublayers read the stream itself and the norms stand on their
+    OUTPUTS.  A sublayer leaves float32 rows of its own (written where it says `can_store`, else added into zeros) and
+    the norm's `add_normed` takes them into the stream; a mixer that says `reads_stream` gets the float32 rows
+    themselves, any other part a copy in the activation dtype (which the first norm leaves behind for the feed-forward)."""
+    for norm in (block.norm1, block.norm2 if block.ffn is not None else block.norm1):
+        if norm is None or not hasattr(norm, "add_normed"):
+            raise ConfigError("the 'outnorm' arrangement needs norms that offer add_normed (layernorm)")
+    h = x if getattr(block.mixer, "reads_stream", False) else ops.cast_rows(x, act_dtype)
+    if getattr(block.mixer, "can_store", False):
+        y = block.mixer.forward(h, ctx, cache, torch.empty_like(x), reads_only=reads_only, store=True)
+    else:
+        y = block.mixer.forward(h, ctx, cache, torch.zeros_like(x), reads_only=reads_only)
+    if block.ffn is None:
+        block.norm1.add_normed(x, y)
+        return
+    h = x if act_dtype == torch.float32 else torch.empty(x.shape, dtype=act_dtype, device=x.device)
+    block.norm1.add_normed(x, y, cast=None if h is x else h)
+    if getattr(block.ffn, "can_store", False):
+        y = block.ffn.forward(h, ctx, y, store=True)
+    else:
+        y = block.ffn.forward(h, ctx, y.zero_())
+    block.norm2.add_normed(x, y)
+
+
 def _with_children(part):
     return [part] + [q for c in part.children() for q in _with_children(c)]
 
@@ -250,9 +276,10 @@ class Model:
         return chain + self.head.weight_order()
 
     def cache_needs(self):
-        """Per schedule entry: the mixer's cache need, or None when the entry reads another's."""
-        return [None if run.cache_of is not None else self.blocks[run.layer].mixer.cache_need()
-                for run in self.schedule]
+        """Per schedule entry: the mixer's cache need; when the entry reads another's, what it still keeps of its own
+        (mostly None)."""
+        return [self.blocks[run.layer].mixer.private_need() if run.cache_of is not None
+                else self.blocks[run.layer].mixer.cache_need() for run in self.schedule]
 
     # ---- the step's body
     def forward(self, ctx, caches, greedy_tokens=None) -> torch.Tensor:
@@ -272,7 +299,10 @@ class Model:
                 norm_after = self.blocks[self.schedule[n + 1].layer].norm1
             else:
                 norm_after = self.final_norm if (ctx.logits_all and ctx.n_logit_rows) else None
-            self.blocks[run.layer].forward(x, ctx, caches[src], self.act_dtype,
+            cache = caches[src]
+            if run.cache_of is not None and caches[n] is not None:
+                cache = (caches[n], cache)          # what the entry keeps of its own, and the entry it reads
+            self.blocks[run.layer].forward(x, ctx, cache, self.act_dtype,
                                            reads_only=run.cache_of is not None, norm_after=norm_after)
             if self.after_run is not None:
                 self.after_run(n, x)

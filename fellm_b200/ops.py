@@ -142,6 +142,92 @@ def rmsnorm(x, w, eps: float, out_dtype, rows=None, out=None):
     return out
 
 
+# ------------------------------------------------------------------------------ norms on a sublayer's output
+
+def layernorm(x, w, b, eps: float, out_dtype, rows=None, out=None):
+    """x float32 [T, d] -> (x - mean) / sqrt(var + eps) * w + b, [T or len(rows), d] in out_dtype (var: the mean of the
+    squared deviations; w, b float32 [d])."""
+    _dev(x, w, b, rows)
+    assert x.dtype == torch.float32 and w.dtype == torch.float32 and b.dtype == torch.float32 and x.is_contiguous()
+    d = x.shape[-1]
+    assert w.numel() == d and b.numel() == d
+    n = x.shape[0] if rows is None else rows.numel()
+    if rows is not None:
+        _i32(rows, "rows")
+    if out is None:
+        out = torch.empty((n, d), dtype=out_dtype, device=x.device)
+    f = _fn("sublayer", "fellm_layernorm", [_c_p, _c_p, _c_p, _c_p, _c_int, _c_p, _c_int, _c_int, _c_f, _c_p])
+    _check(f(_p(x), _p(w), _p(b), _p(out), _is_bf16(out), _p(rows), n, d, float(eps), _stream()), "layernorm")
+    return out
+
+
+def add_layernorm(x, y, w, b, eps: float, cast=None):
+    """x float32 [T, d] += LN(y) (y float32 [T, d], weight and bias float32 [d]).  cast [T, d] (bfloat16 or float32):
+    also receives the new rows of x in its dtype."""
+    _dev(x, y, w, b, cast)
+    T, d = x.shape
+    assert x.dtype == torch.float32 and y.dtype == torch.float32 and x.is_contiguous() and y.is_contiguous() and y.shape == x.shape
+    assert w.dtype == torch.float32 and b.dtype == torch.float32 and w.numel() == d and b.numel() == d
+    if cast is not None:
+        assert cast.is_contiguous() and cast.shape == x.shape
+    residual_written(x)
+    f = _fn("sublayer", "fellm_add_layernorm", [_c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_f, _c_p])
+    _check(f(_p(x), _p(y), _p(w), _p(b), _p(cast), _is_bf16(cast) if cast is not None else 0, T, d, float(eps), _stream()),
+           "add_layernorm")
+    return x
+
+
+def cast_rows(x, out_dtype, out=None):
+    """float32 rows in the activation dtype (the tensor itself where that is float32)."""
+    if out_dtype == torch.float32:
+        return x
+    _dev(x)
+    assert x.dtype == torch.float32 and x.is_contiguous() and out_dtype == torch.bfloat16
+    if out is None:
+        out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    f = _fn("sublayer", "fellm_cast_rows", [_c_p, _c_p, _c_ll, _c_p])
+    _check(f(_p(x), _p(out), x.numel(), _stream()), "cast_rows")
+    return out
+
+
+GLU_ACTS = {"silu": 0, "gelu_tanh": 1}
+
+
+def act_mul(gu, act: str, out=None):
+    """gu [T, >= 2F] (gate | up, row stride free) -> [T, F] = act(gate) * up; act 'silu' or 'gelu_tanh'
+    (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))))."""
+    _dev(gu)
+    assert gu.stride(1) == 1 and gu.shape[1] % 2 == 0
+    if act not in GLU_ACTS:
+        raise KernelError(f"act_mul: unknown activation {act!r}")
+    T, F = gu.shape[0], gu.shape[1] // 2
+    if out is None:
+        out = torch.empty((T, F), dtype=gu.dtype, device=gu.device)
+    f = _fn("sublayer", "fellm_act_mul", [_c_p, _c_int, _c_p, _c_int, _c_int, _c_int, _c_int, _c_p])
+    _check(f(_p(gu), gu.stride(0), _p(out), _is_bf16(gu), T, F, GLU_ACTS[act], _stream()), "act_mul")
+    return out
+
+
+def gate_mul(a, g):
+    """a [T, N] *= sigmoid(g) in place, g [T, N] of a's dtype (row stride free)."""
+    _dev(a, g)
+    assert a.is_contiguous() and g.stride(1) == 1 and g.dtype == a.dtype and g.shape == a.shape
+    f = _fn("sublayer", "fellm_gate_mul", [_c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_p])
+    _check(f(_p(a), _p(g), g.stride(0), _is_bf16(a), a.shape[0], a.shape[1], _stream()), "gate_mul")
+    return a
+
+
+def relu2(z, out_dtype, out=None):
+    """float32 z -> max(z, 0)^2 in out_dtype."""
+    _dev(z)
+    assert z.dtype == torch.float32 and z.is_contiguous()
+    if out is None:
+        out = torch.empty(z.shape, dtype=out_dtype, device=z.device)
+    f = _fn("sublayer", "fellm_relu2", [_c_p, _c_p, _c_int, _c_ll, _c_p])
+    _check(f(_p(z), _p(out), _is_bf16(out), z.numel(), _stream()), "relu2")
+    return out
+
+
 def silu_mul(gu, out=None):
     """gu [T, 2F] (gate | up) -> [T, F] = silu(gate) * up."""
     _dev(gu)
@@ -505,6 +591,47 @@ def token_shift_mix(h, mu, state, item_start, item_slot, n_items, max_item_rows,
     return out
 
 
+def token_shift(x, mu, state, item_start, item_slot, n_items, max_item_rows, out_dtype, out=None):
+    """x float32 [T, d] -> x + (x_prev - x) * mu in out_dtype, x_prev the row before (the slot's float32 state [slots, d]
+    before a portion's first row; the state then takes the portion's last row of x as it is)."""
+    _dev(x, mu, state, item_start, item_slot)
+    T, d = x.shape
+    assert x.dtype == torch.float32 and x.is_contiguous() and mu.dtype == torch.float32 and mu.numel() == d and mu.is_contiguous()
+    assert state.shape[1:] == (d,)
+    _i32(item_start, "item_start"), _i32(item_slot, "item_slot")
+    if out is None:
+        out = torch.empty((T, d), dtype=out_dtype, device=x.device)
+    sp, ss = _state_args(state)
+    f = _fn("recurrent", "fellm_token_shift", [_c_p, _c_p, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p])
+    _check(f(_p(x), _p(mu), sp, ss, _p(item_start), _p(item_slot), _p(out), _is_bf16(out), T, n_items, d, int(max_item_rows),
+             _stream()), "token_shift")
+    return out
+
+
+def gated_write_scan(z, f_off, v_off, lower, bias, state, item_start, item_slot, n_items, H, dk, dv, out=None,
+                     max_item_rows=0):
+    """Per head S = diag(f) S + (1 - f) v^T, o = S^T q, with q = SiLU(q raw) and f = lower + (1 - lower) sigmoid(f raw +
+    bias).  z float32 [T, >= v_off + H*dv]: q raw at column 0 (H x dk), f raw at f_off, v at v_off (H x dv); lower, bias
+    float32 [H*dk]; state float32 [slots, H, dk, dv] (the scan kernel's own layout).  Returns float32 [T, H*dv]."""
+    _dev(z, lower, bias, state, item_start, item_slot)
+    T = z.shape[0]
+    if dk > MAX_SCAN_KEY_DIM:
+        raise KernelError(f"gated_write_scan: key size {dk} is above the kernel's {MAX_SCAN_KEY_DIM}")
+    assert z.dtype == torch.float32 and z.stride(1) == 1 and z.shape[1] >= v_off + H * dv
+    for v in (lower, bias):
+        assert v.dtype == torch.float32 and v.numel() == H * dk and v.is_contiguous()
+    assert state.shape[1:] == (H, dk, dv)
+    _i32(item_start, "item_start"), _i32(item_slot, "item_slot")
+    if out is None:
+        out = torch.empty((T, H * dv), dtype=torch.float32, device=z.device)
+    sp, ss = _state_args(state)
+    f = _fn("recurrent", "fellm_gated_write_scan",
+            [_c_p, _c_int, _c_int, _c_int, _c_p, _c_p, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p])
+    _check(f(_p(z), z.stride(0), int(f_off), int(v_off), _p(lower), _p(bias), sp, ss, _p(item_start), _p(item_slot), _p(out),
+             n_items, H, dk, dv, int(max_item_rows), _stream()), "gated_write_scan")
+    return out
+
+
 _LR_IN = {"none": 0, "tanh": 1}
 _LR_OUT = {"none": 0, "exp_neg_exp": 1, "decay_softplus": 2}
 
@@ -703,13 +830,16 @@ def moe_route(logits, E: int, top: int, renormalize: bool = False):
 
 
 def moe_router(h, w_router, top: int, renormalize: bool = False, *, score: str = "softmax", correction=None,
-               groups=None):
+               groups=None, bias=None):
     """The router's product and the routing in one launch: z = h W_router^T in float32 (h [T, K] and W_router [E, K]
     bfloat16 or float32), then as moe_route.  score = "sigmoid": the scores are sigmoid(z); the choice looks at
     score + correction (float32 [E]) and, with groups = (count, keep, best), only inside the `keep` of `count` equal
     groups of neighbouring experts whose `best` largest choice scores sum highest; the weights are the plain scores
-    (renormalize: over their sum + 1e-20).  Returns (idx int32 [T, top], w float32 [T, top])."""
-    _dev(h, w_router, correction)
+    (renormalize: over their sum + 1e-20).  bias float32 [E]: added to z first.  Softmax scores renormalised over the
+    chosen are the softmax over the chosen logits alone.  Returns (idx int32 [T, top], w float32 [T, top])."""
+    _dev(h, w_router, correction, bias)
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.numel() == w_router.shape[0] and bias.is_contiguous()
     assert h.stride(1) == 1 and w_router.is_contiguous() and h.shape[1] == w_router.shape[1]
     T, K = h.shape
     E = w_router.shape[0]
@@ -725,9 +855,10 @@ def moe_router(h, w_router, top: int, renormalize: bool = False, *, score: str =
     idx = torch.empty((T, top), dtype=torch.int32, device=h.device)
     w = torch.empty((T, top), dtype=torch.float32, device=h.device)
     f = _fn("moe", "fellm_moe_router", [_c_p, _c_int, _c_int, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p, _c_p,
-                                        _c_int, _c_p, _c_int, _c_int, _c_int, _c_p])
+                                        _c_int, _c_p, _c_int, _c_int, _c_int, _c_p, _c_p])
     _check(f(_p(h), _is_bf16(h), h.stride(0), _p(w_router), _is_bf16(w_router), T, K, E, top, int(renormalize), _p(idx),
-             _p(w), int(score == "sigmoid"), _p(correction), int(n_groups), int(keep), int(best), _stream()), "moe_router")
+             _p(w), int(score == "sigmoid"), _p(correction), int(n_groups), int(keep), int(best), _p(bias), _stream()),
+           "moe_router")
     return idx, w
 
 
@@ -859,6 +990,26 @@ def qk_rope_write(qkv, q_w, k_w, eps, inv_freq, pairing, positions, row_slot, bl
              _is_bf16(pool) if write_kv else _is_bf16(qkv), layer, pool.shape[1] if write_kv else 1,
              page_tokens, _p(q_out), T, H, G, hd, rot_dim, int(write_kv), _p(status), _stream()), "qk_rope_write")
     return q_out
+
+
+def qk_rotate_norm(qkv, n_q, n_k, k_off, hd, rot_dim, inv_freq, pairing, positions, eps, unit_norm=True):
+    """In place on the rows of qkv [T, *]: the n_q heads at column 0 and the n_k heads at column k_off (hd each) are rotated
+    by position on their first rot_dim elements (inv_freq float32 [rot_dim/2], or None for no rotation) and then, with
+    unit_norm, divided by their root mean square over hd (eps inside the root; no weight)."""
+    _dev(qkv, inv_freq, positions)
+    assert qkv.stride(1) == 1
+    _i32(positions, "positions")
+    rot_dim = 0 if inv_freq is None else int(rot_dim)
+    if hd > 512 or rot_dim % 2 or not 0 <= rot_dim <= hd:
+        raise KernelError(f"qk_rotate_norm: head size {hd} (at most 512) / rotated part {rot_dim} (even, within the head)")
+    if inv_freq is not None:
+        assert inv_freq.dtype == torch.float32 and inv_freq.numel() == rot_dim // 2 and inv_freq.is_contiguous()
+    assert qkv.shape[1] >= max(n_q * hd, k_off + n_k * hd if n_k else 0)
+    f = _fn("qk_rope_write", "fellm_qk_rotate_norm",
+            [_c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p, _c_int, _c_p, _c_f, _c_int, _c_p])
+    _check(f(_p(qkv), _is_bf16(qkv), qkv.stride(0), qkv.shape[0], int(n_q), int(n_k), int(k_off), int(hd), rot_dim,
+             _p(inv_freq), PAIRINGS[pairing], _p(positions), float(eps), int(unit_norm), _stream()), "qk_rotate_norm")
+    return qkv
 
 
 def paged_attention_simt(q, pool, block_table, positions, row_slot, layer, scale, window=None, out=None):

@@ -151,6 +151,11 @@ class Mixer(Part):
         forward() is then a list of views in the same order."""
         return None
 
+    def private_need(self):
+        """What the mixer keeps of its OWN even where its schedule entry reads another entry's cache (Run.cache_of): None,
+        or needs as cache_need() gives them.  forward() then gets `cache` = (views of these, the other entry's views)."""
+        return None
+
     def forward(self, xn: torch.Tensor, ctx, cache, out: torch.Tensor, reads_only: bool = False):
         """xn: [T, d] normed input in the engine's dtype; `out`: float32 [T, d] residual stream,
         to which the mixer ADDS its result in place.  `cache` is this run's view of its cache

@@ -11,6 +11,10 @@ largest choice scores sum highest; the weights stay the plain s (renormalize: ov
 act=("clamped", limit, alpha) an expert computes min(g, limit) sigmoid(alpha min(g, limit)) (clamp(u, -limit, limit) + 1)
 in place of SiLU(g) u.
 
+With router_bias=True the logits are z = W_router h + b (b a tensor of the layer).  With renormalize=True the softmax
+scores over their sum ARE the softmax over the chosen logits alone.  With plain="relu2" an expert has no gate:
+W_down relu(W_up h)^2 (the first grouped product leaves float32 rows, ops.relu2 squares them into the activation dtype).
+
 Experts have no biases.  Nothing goes through the host: the router's choices are sorted by expert on the device
 (ops.moe_plan; the router's product and the routing are one launch, ops.moe_router) and two grouped products walk
 the sorted rows (tcgen05 for steps of many rows, mma.sync tiles between, a warp a column for a handful of tokens), the first gathering its input rows by token and
@@ -30,7 +34,8 @@ from .linear import linear_modules
 @register_part("feed_forward", "moe")
 class RoutedExperts(FeedForward):
     def __init__(self, *, dtype: str, size: int, ff: int, experts: int, top: int, renormalize: bool = False,
-                 score: str = "softmax", correction: bool = False, groups=None, act=None):
+                 score: str = "softmax", correction: bool = False, groups=None, act=None, router_bias: bool = False,
+                 plain=None):
         super().__init__()
         self.size, self.ff, self.E, self.top = int(size), int(ff), int(experts), int(top)
         self.renormalize = bool(renormalize)
@@ -54,16 +59,33 @@ class RoutedExperts(FeedForward):
             if kind != "clamped" or not float(limit) > 0.0:
                 raise ConfigError(f"moe: unknown expert activation {act!r} (('clamped', limit > 0, alpha))")
             self.act = (float(limit), float(alpha))
+        if plain not in (None, "relu2"):
+            raise ConfigError(f"moe: unknown activation of plain experts {plain!r} (relu2)")
+        if plain and act:
+            raise ConfigError("moe: plain experts have no gated activation")
+        self.plain = plain
         self.decls = {"router.weight": ParamDecl((self.E, self.size), init=("normal", 0.5))}
+        if router_bias:
+            self.decls["router.bias"] = ParamDecl((self.E,), role="vector", init=("normal", 0.5))
         if correction:
             self.decls["correction"] = ParamDecl((self.E,), role="vector", init=("normal", 0.2))
         for e in range(self.E):
-            self.decls[f"e{e}.gate.weight"] = ParamDecl((self.ff, self.size))
+            if not self.plain:
+                self.decls[f"e{e}.gate.weight"] = ParamDecl((self.ff, self.size))
             self.decls[f"e{e}.up.weight"] = ParamDecl((self.ff, self.size))
             self.decls[f"e{e}.down.weight"] = ParamDecl((self.size, self.ff))
 
     def prepare(self):
         w = self.w
+        if self.plain:
+            ups = [w.pop(f"e{e}.up.weight") for e in range(self.E)]
+            downs = [w.pop(f"e{e}.down.weight") for e in range(self.E)]
+            dt = ups[0].dtype if all(m.dtype == ups[0].dtype for m in ups + downs) else torch.float32
+            self.interleaved = False
+            w["up.weight"] = torch.stack([m.to(dt) for m in ups], 0).contiguous()          # [E, ff, d]
+            w["down.weight"] = torch.stack([m.to(dt) for m in downs], 0).contiguous()      # [E, d, ff]
+            w["router.weight"] = w["router.weight"].contiguous()
+            return
         mats = [w.pop(f"e{e}.{n}.weight") for e in range(self.E) for n in ("gate", "up", "down")]
         dt = mats[0].dtype if all(m.dtype == mats[0].dtype for m in mats) else torch.float32
         # on the tensor-core paths an expert's gate and up rows lie in blocks of 8 by turns, as the dense feed-forward's do
@@ -79,19 +101,26 @@ class RoutedExperts(FeedForward):
     def forward(self, hn, ctx, out):
         w = self.w
         idx, score = ops.moe_router(hn, w["router.weight"], self.top, self.renormalize, score=self.score,
-                                    correction=w.get("correction"), groups=self.groups)
-        if hn.dtype != w["gate_up.weight"].dtype:          # a file that stores some experts in 32-bit under a bfloat16 engine
-            hn = hn.to(w["gate_up.weight"].dtype)
+                                    correction=w.get("correction"), groups=self.groups, bias=w.get("router.bias"))
+        first = w["up.weight"] if self.plain else w["gate_up.weight"]
+        if hn.dtype != first.dtype:          # a file that stores some experts in 32-bit under a bfloat16 engine
+            hn = hn.to(first.dtype)
         bf = hn.dtype == torch.bfloat16
-        tile = ops.moe_row_tile(idx.numel(), bf, self.interleaved and self.ff % 8 == 0 and self.size % 8 == 0 and hn.stride(0) % 8 == 0)
+        k_ok = self.ff % 8 == 0 and self.size % 8 == 0 and hn.stride(0) % 8 == 0
+        tile = ops.moe_row_tile(idx.numel(), bf, k_ok and (self.interleaved or bool(self.plain)))
         plan = ops.moe_plan(idx, self.E, tile)
+        if self.plain:
+            a = ops.relu2(ops.moe_gemm(hn, first, plan, gated=False, gather=True), hn.dtype)
+            y = ops.moe_gemm(a, w["down.weight"], plan, gated=False, gather=False)
+            ops.moe_combine(out, y, plan, score)
+            return out
         a = ops.moe_gemm(hn, w["gate_up.weight"], plan, gated=True, gather=True, interleaved=self.interleaved, act=self.act)
         y = ops.moe_gemm(a, w["down.weight"], plan, gated=False, gather=False)
         ops.moe_combine(out, y, plan, score)
         return out
 
     def weight_order(self):
-        return [self.w["router.weight"], self.w["gate_up.weight"], self.w["down.weight"]]
+        return [self.w["router.weight"], self.w["up.weight" if self.plain else "gate_up.weight"], self.w["down.weight"]]
 
     def kernel_modules(self, dtype):
-        return linear_modules(dtype) + [("moe", None)]
+        return linear_modules(dtype) + [("moe", None)] + ([("sublayer", None)] if self.plain else [])

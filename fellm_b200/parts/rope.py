@@ -8,7 +8,11 @@ pair(t) = rot_dim ln(original / (2 pi t)) / (2 ln theta), the pair index at whic
 `original` positions, lo = max(floor(pair(fast)), 0), hi = min(ceil(pair(slow)), rot_dim - 1) and
 ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), pair i turns at f_i / factor * ramp_i + f_i (1 - ramp_i):
 fast pairs keep their frequency, slow ones are divided by the factor.  `magnitude` = 0.1 ln(factor) + 1 then
-multiplies cos and sin (1 without scaling); a kernel that rotates takes it beside inv_freq."""
+multiplies cos and sin (1 without scaling); a kernel that rotates takes it beside inv_freq.
+
+Frequencies rescaled by wavelength (`bands` = (factor, low, high, original)): with l = 2 pi / f, a pair keeps f where
+l < original / high, turns at f / factor where l > original / low, and between the two, with
+s = (original / l - low) / (high - low), at (1 - s) f / factor + s f.  No magnitude goes with it."""
 from __future__ import annotations
 
 import math
@@ -32,7 +36,8 @@ class NoPosition(PositionEncoding):
 
 @register_part("position", "rope")
 class Rotary(PositionEncoding):
-    def __init__(self, *, dtype: str, rot_dim: int, theta: float, pairing: str, table64: bool = False, scaling=None):
+    def __init__(self, *, dtype: str, rot_dim: int, theta: float, pairing: str, table64: bool = False, scaling=None,
+                 bands=None):
         """table64: the frequencies are computed in float64 and rounded once (default: float32 powers, as FeLLM's).
         scaling: (factor, original, fast, slow), see the module's head; computed in float64 and rounded once."""
         super().__init__()
@@ -42,6 +47,25 @@ class Rotary(PositionEncoding):
         if pairing not in ("adjacent", "split_half"):
             raise ConfigError(f"unknown rotary pairing {pairing!r}")
         self.rot_dim, self.theta, self.pairing = int(rot_dim), float(theta), pairing
+        if bands and scaling:
+            raise ConfigError("rotary: `scaling` and `bands` are two ways to rescale the frequencies; name one")
+        if bands:
+            factor, low, high, original = (float(v) for v in bands)
+            if min(factor, low, high, original) <= 0 or self.theta <= 0:
+                raise ConfigError(f"rotary bands {bands!r} need positive numbers")
+            freqs = []
+            for i in range(self.rot_dim // 2):          # float64 on the host, rounded once
+                f = self.theta ** (-2.0 * i / self.rot_dim)
+                wavelength = 2.0 * math.pi / f
+                if wavelength < original / high:
+                    freqs.append(f)
+                elif wavelength > original / low:
+                    freqs.append(f / factor)
+                else:
+                    s = (original / wavelength - low) / ((high - low) or 1.0)
+                    freqs.append((1.0 - s) * f / factor + s * f)
+            self.inv_freq = torch.tensor(freqs, dtype=torch.float64).to(torch.float32)
+            return
         if scaling:
             factor, original, fast, slow = (float(v) for v in scaling)
             if min(factor, original, fast, slow) <= 0 or self.theta <= 1.0:

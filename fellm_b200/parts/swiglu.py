@@ -1,19 +1,25 @@
 """SwiGLU feed-forward: f = W_down (silu(W_gate h) * (W_up h)), silu(g) = g/(1+exp(-g))
-(crates/fellm-model/src/graph.rs:2260-2287; crates/backend-cpu/src/kernels/swiglu.rs:4-16)."""
+(crates/fellm-model/src/graph.rs:2260-2287; crates/backend-cpu/src/kernels/swiglu.rs:4-16).
+
+`act="gelu_tanh"`: the gate's activation is 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))) instead (one product for
+gate and up, the activation in a kernel of its own, ops.act_mul)."""
 from __future__ import annotations
 
 import torch
 
 from .. import ops
+from ..config.errors import ConfigError
 from .base import FeedForward, ParamDecl, register_part
 from .linear import LazyNorm, linear, linear_modules
 
 
 @register_part("feed_forward", "swiglu")
 class SwiGLU(FeedForward):
-    def __init__(self, *, dtype: str, size: int, ff: int):
+    def __init__(self, *, dtype: str, size: int, ff: int, act: str = "silu"):
         super().__init__()
-        self.size, self.ff = int(size), int(ff)
+        self.size, self.ff, self.act = int(size), int(ff), str(act)
+        if self.act not in ops.GLU_ACTS:
+            raise ConfigError(f"gated feed-forward: unknown activation {act!r} ({', '.join(ops.GLU_ACTS)})")
         self.decls = {"gate.weight": ParamDecl((self.ff, self.size)),
                       "up.weight": ParamDecl((self.ff, self.size)),
                       "down.weight": ParamDecl((self.size, self.ff))}
@@ -25,7 +31,8 @@ class SwiGLU(FeedForward):
         g, u = self.w.pop("gate.weight"), self.w.pop("up.weight")
         if g.dtype != u.dtype:
             g, u = g.float(), u.float()
-        self.fused = (g.dtype == torch.bfloat16 and g.is_cuda and self.ff % 8 == 0 and self.size % 8 == 0)
+        self.fused = (g.dtype == torch.bfloat16 and g.is_cuda and self.ff % 8 == 0 and self.size % 8 == 0
+                      and self.act == "silu")
         if self.fused:
             self.w["gate_up.weight"] = ops.interleave_gate_up(g, u)
         else:
@@ -33,16 +40,20 @@ class SwiGLU(FeedForward):
 
     takes_lazy_norm = True
 
-    def forward(self, hn, ctx, out):
+    can_store = True          # forward(store=True) writes its rows instead of adding them
+
+    def forward(self, hn, ctx, out, store=False):
         if self.fused:
             z = linear(hn, self.w["gate_up.weight"], swiglu=True)
-        else:
+        elif self.act == "silu":
             z = ops.silu_mul(linear(hn, self.w["gate_up.weight"]))
-        linear(z, self.w["down.weight"], out=out, accumulate=True)
+        else:
+            z = ops.act_mul(linear(hn, self.w["gate_up.weight"]), self.act)
+        linear(z, self.w["down.weight"], out=out, accumulate=not store)
         return out
 
     def weight_order(self):
         return [self.w["gate_up.weight"], self.w["down.weight"]]
 
     def kernel_modules(self, dtype):
-        return linear_modules(dtype) + [("elementwise", None)]
+        return linear_modules(dtype) + [("elementwise", None)] + ([("sublayer", None)] if self.act != "silu" else [])
