@@ -191,7 +191,9 @@ def distance(got, want) -> float:
     return float(row_distances(got, want).max())
 
 
-LIMIT = {"float32": 1e-4, "bfloat16": 6e-2}
+# (bfloat16: these models are 72 to 144 wide and norm every sublayer's OUTPUT: the rounding of a product of so few terms does
+# not average out, and a small output is divided by its own size; the float32 engine is the sharp comparison)
+LIMIT = {"float32": 1e-4, "bfloat16": 1e-1}
 
 
 def assert_close(got, want, dtype: str, times: float = 1.0, note=None):

@@ -68,11 +68,12 @@ def rotary_frequencies(dims, base, scaling=None):
 
 
 def rotate(x, pos, freqs):
-    """x [heads, size]: the first 2 len(freqs) elements of each head are rotated, element i with i + len(freqs)."""
+    """x [heads, size]: the first 2 len(freqs) elements of each head are rotated, element i with i + len(freqs).  Positions,
+    frequencies and their product are float32 numbers (the design computes angles in 32-bit); the rest is float64."""
     n = len(freqs)
     if n == 0:
         return x
-    a = pos * freqs
+    a = (np.float32(pos) * np.asarray(freqs, dtype=np.float32)).astype(np.float64)      # the angle is a float32 product
     c, s = np.cos(a), np.sin(a)
     out = x.copy()
     u, v = x[:, :n], x[:, n:2 * n]
