@@ -366,9 +366,33 @@ def meresun_config(width, ff, layers, vocab):
                 layers=[dict(type="latent_attention", mixer=mix, mlp=moe if i % 2 else dense) for i in range(layers)])
 
 
-DESIGNS = {"robazen": robazen_config, "samusun": samusun_config, "meresun": meresun_config}
+def nalizen_config(width, ff, layers, vocab):
+    """A Nalizen model of real-looking layers at this width: HGRN2 layers with heads of 128 x 128, one per 128 of width, and
+    attention layers with heads of 64 (four per key head), half of a head rotated with frequencies rescaled beyond 4,096
+    positions, a window of 1,024 positions, every second attention layer reading the keys and values of the one before it;
+    feed-forwards by turns dense (`ff`, gated) and routed (8 plain experts of ff / 2, two a token); a LayerNorm on every
+    sublayer's output, the token shift in front of every mixer, a side input of 64 a token and layer."""
+    H = max(width // 64, 1)
+    att = dict(dim=64, heads=H, kv_heads=max(H // 4, 1), mask=dict(size=1024), scale=0.125, vdim=64,
+               rot=dict(base=10000.0, dims=32, scaling=dict(factor=8.0, high=4.0, low=1.0, original=4096)))
+    rec = dict(dim=128, heads=max(width // 128, 1), vdim=128)
+    dense = dict(ff=ff, kind="dense")
+    moe = dict(expert=dict(ff=ff // 2), kind="moe", router=dict(experts=8, top=2))
+    out = []
+    for i in range(layers):
+        if i % 4 == 1:
+            out.append(dict(type="attention", mixer=att, mlp=moe))
+        elif i % 4 == 3:
+            out.append(dict(type="attention", mixer=dict(att, kv_from=i - 2), mlp=moe))
+        else:
+            out.append(dict(type="hgrn2", mixer=rec, mlp=dense))
+    return dict(architecture="Nalizen", embedding=dict(scale=1.0), vocab=vocab, width=width, norm=dict(eps=1e-5),
+                token_side=dict(dim=64), layers=out)
+
+
+DESIGNS = {"robazen": robazen_config, "samusun": samusun_config, "meresun": meresun_config, "nalizen": nalizen_config}
 # the model a design is measured beside (default: LFM2 of the same width, depth, feed-forward and vocabulary)
-BESIDE = {"meresun": "samusun"}
+BESIDE = {"meresun": "samusun", "nalizen": "samusun"}
 
 
 def run_design(design, shapes, layers, batches, steps, warmup):
@@ -560,7 +584,7 @@ def main():
     ap.add_argument("--context", type=int, default=PROMPT)
     ap.add_argument("--design", choices=sorted(DESIGNS), default=None,
                     help="prefill and decode throughput of this design at a few real-looking sizes beside the closest model of "
-                         "equal width, depth and feed-forward (LFM2; Samusun for meresun) (--layers layers, default 8; --steps decode steps, default 64); "
+                         "equal width, depth and feed-forward (LFM2; Samusun for meresun and nalizen) (--layers layers, default 8; --steps decode steps, default 64); "
                          "prints one line of its own and leaves the headline measurement alone")
     args = ap.parse_args()
 
