@@ -636,21 +636,21 @@ FELLM_API int fellm_moe_gather(const void* a, int lda, const int* sorted, int to
 }
 
 // ---------------------------------------------------------------- the weighted sum into the residual stream
-// x[t, :] += sum_c w[t, c] * y[place_of[t * top + c], :], c = 0 .. top-1 in order, float32.
+// x[t, :] += sum_c w[t, c] * y[place_of[t * top + c], :], c = 0 .. top-1 in order, float32 (store: x[t, :] = the sum).
 __global__ void moe_combine_kernel(float* __restrict__ x, const float* __restrict__ y, const int* __restrict__ place_of,
-                                   const float* __restrict__ w, int top, int d) {
+                                   const float* __restrict__ w, int top, int d, int store) {
   const int t = blockIdx.x;
   for (int i = threadIdx.x; i < d; i += blockDim.x) {
     float s = 0.f;
     for (int c = 0; c < top; ++c) s = fmaf(w[(size_t)t * top + c], y[(size_t)place_of[(size_t)t * top + c] * d + i], s);
-    x[(size_t)t * d + i] += s;
+    x[(size_t)t * d + i] = store ? s : x[(size_t)t * d + i] + s;
   }
 }
 
 FELLM_API int fellm_moe_combine(float* x, const float* y, const int* place_of, const float* w, int T, int top, int d,
-                                cudaStream_t stream) {
+                                int store, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (!x || !y || !place_of || !w) return FELLM_ERR_ARG;
-  moe_combine_kernel<<<T, d >= 256 ? 256 : 128, 0, stream>>>(x, y, place_of, w, top, d);
+  moe_combine_kernel<<<T, d >= 256 ? 256 : 128, 0, stream>>>(x, y, place_of, w, top, d, store);
   return launch_status();
 }

@@ -299,6 +299,63 @@ qk_rotate_norm_kernel(TA* __restrict__ qkv, int ld, int T, int n_q, int n_k, int
   }
 }
 
+// bfloat16, heads of 32, 64, 128 or 256, pairs (i, i + rot_dim/2), rot_dim a multiple of 16: hd / 8 lanes a head, a lane
+// eight consecutive elements (one 16-byte load, and one more for the eight it is paired with); a head's sum of squares
+// goes round its lanes by shuffles.  All loads of a warp lie in front of its stores.
+template <int LANES>
+__global__ void __launch_bounds__(128)
+qk_rotate_norm_vec_kernel(bf16* __restrict__ qkv, int ld, int T, int n_q, int n_k, int k_off, int rot_dim,
+                          const float* __restrict__ inv_freq, const int* __restrict__ positions, float eps, int unit_norm) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int hd = LANES * 8;
+  const long long slot = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / LANES;
+  const int c = threadIdx.x % LANES;                       // this lane's chunk of eight in the head
+  const int heads = n_q + n_k;
+  const bool live = slot < (long long)T * heads;
+  const int row = live ? (int)(slot / heads) : 0, head = live ? (int)(slot - (long long)row * heads) : 0;
+  bf16* p = qkv + (size_t)row * ld + (head < n_q ? (size_t)head * hd : (size_t)k_off + (size_t)(head - n_q) * hd);
+  const int half = rot_dim >> 1, hc = half >> 3;           // chunks of a half
+  float v[8], w[8];
+  uint4 mine = make_uint4(0, 0, 0, 0), other = make_uint4(0, 0, 0, 0);
+  const bool rotated = c < 2 * hc, first = c < hc;
+  if (live) {
+    mine = *(const uint4*)(p + 8 * c);
+    if (rotated) other = *(const uint4*)(p + 8 * (first ? c + hc : c - hc));
+  }
+  __syncwarp();
+  {
+    const __nv_bfloat162* m2 = (const __nv_bfloat162*)&mine; const __nv_bfloat162* o2 = (const __nv_bfloat162*)&other;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 a = __bfloat1622float2(m2[e]), b = __bfloat1622float2(o2[e]);
+      v[2 * e] = a.x; v[2 * e + 1] = a.y; w[2 * e] = b.x; w[2 * e + 1] = b.y;
+    }
+  }
+  float ss = 0.f;
+  if (rotated && live) {
+    const float pos = (float)positions[row];
+    const int f0 = 8 * (first ? c : c - hc);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      float sn, cs;
+      sincosf(pos * inv_freq[f0 + e], &sn, &cs);
+      v[e] = first ? v[e] * cs - w[e] * sn : v[e] * cs + w[e] * sn;
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < 8; ++e) ss = fmaf(v[e], v[e], ss);
+#pragma unroll
+  for (int o = LANES / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  const float scale = unit_norm ? 1.0f / sqrtf(ss / (float)hd + eps) : 1.0f;
+  if (live && (rotated || unit_norm)) {
+    uint4 out; __nv_bfloat162* o2 = (__nv_bfloat162*)&out;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o2[e] = __floats2bfloat162_rn(v[2 * e] * scale, v[2 * e + 1] * scale);
+    *(uint4*)(p + 8 * c) = out;
+  }
+}
+
 FELLM_API int fellm_qk_rotate_norm(void* qkv, int is_bf16, int ld, int T, int n_q, int n_k, int k_off, int hd, int rot_dim,
                                    const float* inv_freq, int pairing, const int* positions, float eps, int unit_norm,
                                    cudaStream_t stream) {
@@ -308,8 +365,22 @@ FELLM_API int fellm_qk_rotate_norm(void* qkv, int is_bf16, int ld, int T, int n_
   if (!qkv || !positions || n_q < 0 || n_k < 0) return FELLM_ERR_ARG;
   if (!rot_dim && !unit_norm) return 0;
   const long long warps = (long long)T * (n_q + n_k);
-  dim3 grid((unsigned)((warps + 3) / 4));
   const int cls = launch_class_for_rows(T, 2);
+  if (is_bf16 && pairing == 1 && (hd == 32 || hd == 64 || hd == 128 || hd == 256) && rot_dim % 16 == 0 && ld % 8 == 0 &&
+      k_off % 8 == 0 && ((uintptr_t)qkv & 15) == 0) {
+    const int lanes = hd / 8;
+    dim3 vgrid((unsigned)((warps * lanes + 127) / 128));
+#define RN_VEC(L_) launch_k_class(cls, qk_rotate_norm_vec_kernel<L_>, vgrid, dim3(128), 0, stream, 1, (bf16*)qkv, ld, T, n_q, n_k, k_off, \
+                                  rot_dim, inv_freq, positions, eps, unit_norm)
+    switch (lanes) {
+      case 4: return RN_VEC(4);
+      case 8: return RN_VEC(8);
+      case 16: return RN_VEC(16);
+      default: return RN_VEC(32);
+    }
+#undef RN_VEC
+  }
+  dim3 grid((unsigned)((warps + 3) / 4));
   if (is_bf16) return launch_k_class(cls, qk_rotate_norm_kernel<bf16>, grid, dim3(128), 0, stream, 1, (bf16*)qkv, ld, T, n_q, n_k, k_off, hd,
                                      rot_dim, inv_freq, pairing, positions, eps, unit_norm);
   return launch_k_class(cls, qk_rotate_norm_kernel<float>, grid, dim3(128), 0, stream, 1, (float*)qkv, ld, T, n_q, n_k, k_off, hd,

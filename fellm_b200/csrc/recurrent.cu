@@ -263,6 +263,12 @@ struct ScanArgs {
   const int* pos; const float* inv_freq; int rot; const float* decay_h; float kscale;
   // gated write: the forget gate's lower bound and its bias, [H, dk] each
   const float* lower; const float* fbias;
+  // a portion in blocks of `blk` tokens that run side by side (recurrences whose write does not read the state: S_t =
+  // G_t S_(t-1) + K_t v_t^T is linear in the state in front of it).  phase 1: every block from a state of zeros, no
+  // outputs; it leaves its end state in blk_state [item][block][H][dv][dk] and the product of its G in blk_decay
+  // [item][block][H][dk].  scan_blocks_kernel then walks an item's blocks in order and turns blk_state into the states
+  // IN FRONT of the blocks (and moves the slot's state on).  phase 3: every block again from that state, with outputs.
+  int phase, blk; float* blk_state; float* blk_decay;
 };
 
 template <int VE> __device__ __forceinline__ void load_vec(const float* p, float* out) {
@@ -492,14 +498,30 @@ __global__ void __launch_bounds__(SC_THREADS) scan_kernel(ScanArgs a) {
   const int col_tiles = (a.dv + COLS - 1) / COLS;
   const int h = blockIdx.x / col_tiles, col0 = (blockIdx.x - h * col_tiles) * COLS;
   const int item = blockIdx.y;
-  const int row_begin = a.item_start[item], n = a.item_start[item + 1] - row_begin;
+  int row_begin = a.item_start[item], n = a.item_start[item + 1] - row_begin;
   const int per_buf = a.tc * (4 * DKP + COLS + 4);          // (a multiple of four floats: the second buffer stays 16-byte aligned)
   const bool consumer = warp < SC_CONSUMERS;
   const int ks = lane % KS, cw = warp * CPW + lane / KS;          // (consumers) this thread's lane of rows and column
   const int j = col0 + cw;
   const bool live = consumer && j < a.dv;
   float* Sg = a.state + (size_t)a.item_slot[item] * a.slot_stride + (size_t)h * a.dk * a.dv;
+  constexpr bool BLOCKS = MODE == 4;                       // (the modes that run portions in blocks)
+  const int phase = BLOCKS ? a.phase : 0;
+  float* Dg = nullptr;
+  if (BLOCKS && phase) {
+    const int off = blockIdx.z * a.blk;
+    if (off >= n) return;                                  // (the whole CTA: this item has no such block)
+    row_begin += off; n = min(a.blk, n - off);
+    const size_t at = ((size_t)item * gridDim.z + blockIdx.z) * a.H + h;
+    Sg = a.blk_state + at * a.dk * a.dv;
+    Dg = a.blk_decay + at * a.dk;
+  }
   float S[4 * R4];
+  float Dp[BLOCKS ? 4 * R4 : 1];
+  if (BLOCKS) {
+#pragma unroll
+    for (int e = 0; e < 4 * R4; ++e) Dp[e] = 1.f;
+  }
   // In memory a head's state is kept column by column (element (i, j) at j * dk + i): a thread's four rows are one
   // 16-byte load and a warp's lanes read a column's rows side by side.  Nothing but this kernel reads the layout.
   const bool s_vec = (a.dk & 3) == 0;
@@ -507,7 +529,10 @@ __global__ void __launch_bounds__(SC_THREADS) scan_kernel(ScanArgs a) {
 #pragma unroll
     for (int r4 = 0; r4 < R4; ++r4) {
       const int i0 = 4 * (ks + KS * r4);
-      if (live && s_vec && i0 < a.dk) {
+      if (phase == 1) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) S[4 * r4 + e] = 0.f;
+      } else if (live && s_vec && i0 < a.dk) {
         const float4 t = *(const float4*)(Sg + (size_t)j * a.dk + i0);
         S[4 * r4] = t.x; S[4 * r4 + 1] = t.y; S[4 * r4 + 2] = t.z; S[4 * r4 + 3] = t.w;
       } else {
@@ -580,13 +605,25 @@ __global__ void __launch_bounds__(SC_THREADS) scan_kernel(ScanArgs a) {
           S[4 * r4 + 1] = fmaf(cK[r4].y, u, cG[r4].y * S[4 * r4 + 1]);
           S[4 * r4 + 2] = fmaf(cK[r4].z, u, cG[r4].z * S[4 * r4 + 2]);
           S[4 * r4 + 3] = fmaf(cK[r4].w, u, cG[r4].w * S[4 * r4 + 3]);
+          if (BLOCKS && phase == 1) {
+            Dp[4 * r4] *= cG[r4].x; Dp[4 * r4 + 1] *= cG[r4].y; Dp[4 * r4 + 2] *= cG[r4].z; Dp[4 * r4 + 3] *= cG[r4].w;
+          }
         }
-        if (ks == 0 && live) a.out[(size_t)(row_begin + t0 + t) * ((size_t)a.H * a.dv) + (size_t)h * a.dv + j] = o;
+        if (ks == 0 && live && phase != 1) a.out[(size_t)(row_begin + t0 + t) * ((size_t)a.H * a.dv) + (size_t)h * a.dv + j] = o;
       }
     }
     __syncthreads();
   }
-  if (live) {
+  if (BLOCKS && phase == 1 && consumer && col0 == 0 && cw == 0) {
+#pragma unroll
+    for (int r4 = 0; r4 < R4; ++r4)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i = 4 * (ks + KS * r4) + e;
+        if (i < a.dk) Dg[i] = Dp[4 * r4 + e];
+      }
+  }
+  if (live && phase != 3) {
 #pragma unroll
     for (int r4 = 0; r4 < R4; ++r4) {
       const int i0 = 4 * (ks + KS * r4);
@@ -601,12 +638,39 @@ __global__ void __launch_bounds__(SC_THREADS) scan_kernel(ScanArgs a) {
   }
 }
 
+// The walk between the two passes of a portion in blocks: per item and state element, over the item's blocks in order,
+// S_b = the state in front of block b (written where the block's end state stood), S_(b+1) = D_b S_b + L_b; the slot then
+// holds the state behind the last block.  A thread an element: the order of the sums is the order of the blocks.
+__global__ void __launch_bounds__(256)
+scan_blocks_kernel(float* __restrict__ blk_state, const float* __restrict__ blk_decay, float* __restrict__ state,
+                   long long slot_stride, const int* __restrict__ item_start, const int* __restrict__ item_slot,
+                   int n_blocks, int blk, int H, int dk, int dv) {
+  const int item = blockIdx.y;
+  const size_t per_head = (size_t)dk * dv, per_item = per_head * H;
+  const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= per_item) return;
+  const int h = (int)(e / per_head), i = (int)((e - (size_t)h * per_head) % dk);
+  const int n = item_start[item + 1] - item_start[item];
+  const int nb = (n + blk - 1) / blk;
+  float* slot = state + (size_t)item_slot[item] * slot_stride + e;
+  float S = *slot;
+  for (int b = 0; b < nb; ++b) {
+    const size_t at = (size_t)item * n_blocks + b;
+    float* L = blk_state + at * per_item + e;
+    const float D = blk_decay[(at * H + h) * dk + i], l = *L;
+    *L = S;
+    S = fmaf(D, S, l);
+  }
+  *slot = S;
+}
+
 template <int MODE, typename TA>
 static int scan_launch(ScanArgs& a, int n_items, int max_item_rows, cudaStream_t stream) {
   int KS = 1;
   while (KS < 32 && a.dk > 16 * KS) KS <<= 1;                // up to 16 rows a thread while dk <= 512
-  // more lanes a column while one item's blocks do not fill the device and a lane keeps four rows or more
-  while (KS < 32 && 8 * KS <= a.dk && a.H * ((a.dv * KS + 32 * SC_CONSUMERS - 1) / (32 * SC_CONSUMERS)) < 120) KS <<= 1;
+  // more lanes a column while one item's blocks do not fill the device and a lane keeps four rows or more (a portion in
+  // blocks fills the device by its blocks: it keeps the fewest lanes a column, the most work a thread)
+  while (!a.phase && KS < 32 && 8 * KS <= a.dk && a.H * ((a.dv * KS + 32 * SC_CONSUMERS - 1) / (32 * SC_CONSUMERS)) < 120) KS <<= 1;
   int r4 = (a.dk + 4 * KS - 1) / (4 * KS), R4 = 1;
   while (R4 < r4) R4 <<= 1;
   if (R4 > 8) return FELLM_ERR_SIZE;
@@ -626,8 +690,10 @@ static int scan_launch(ScanArgs& a, int n_items, int max_item_rows, cudaStream_t
   int tc = 40960 / per_tok;
   a.tc = tc < 1 ? 1 : (tc > SC_MAX_TOK ? SC_MAX_TOK : tc);
   if (max_item_rows > 0 && max_item_rows < a.tc) a.tc = max_item_rows;      // a decode step stages one token: 4 KB a block, not 67
+  if (a.phase && a.tc > 8) a.tc = 8;                                        // blocks side by side: less shared memory, more CTAs an SM
   const size_t smem = (size_t)2 * a.tc * per_tok;
-  dim3 grid(a.H * ((a.dv + COLS - 1) / COLS), n_items);
+  const int n_blocks = a.phase ? (max_item_rows + a.blk - 1) / a.blk : 1;
+  dim3 grid(a.H * ((a.dv + COLS - 1) / COLS), n_items, n_blocks);
   void (*kern)(ScanArgs) = nullptr;
 #define SCAN_PICK(R4_, KS_) if (R4 == R4_ && KS == KS_) kern = scan_kernel<MODE, R4_, KS_, TA>
   SCAN_PICK(1, 8); SCAN_PICK(2, 8); SCAN_PICK(4, 8); SCAN_PICK(1, 16); SCAN_PICK(2, 16); SCAN_PICK(4, 16);
@@ -640,6 +706,14 @@ static int scan_launch(ScanArgs& a, int n_items, int max_item_rows, cudaStream_t
     if (e != cudaSuccess) return (int)e;
   }
   kern<<<grid, SC_THREADS, smem, stream>>>(a);
+  if (a.phase == 1) {
+    // the walk over the blocks, then every block again from the state in front of it
+    const size_t per_item = (size_t)a.H * a.dk * a.dv;
+    scan_blocks_kernel<<<dim3((unsigned)((per_item + 255) / 256), n_items), 256, 0, stream>>>(
+        a.blk_state, a.blk_decay, a.state, a.slot_stride, a.item_start, a.item_slot, n_blocks, a.blk, a.H, a.dk, a.dv);
+    a.phase = 3;
+    kern<<<grid, SC_THREADS, smem, stream>>>(a);
+  }
   return launch_status();
 }
 
@@ -695,9 +769,13 @@ FELLM_API int fellm_retention_scan(const void* qkv, int is_bf16, int ld, int k_o
 // Gated write: S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T, o_t = S_t^T q_t with q = SiLU(q raw) and
 // f = lower + (1 - lower) sigmoid(f raw + bias).  z float32 [T, ld]: q raw at column 0 (H x dk), f raw at f_off (H x dk),
 // v at v_off (H x dv), as their product left them; lower, bias float32 [H * dk].
+// blk > 0 (with scratch of n_items * ceil(max_item_rows / blk) * H * (dk * dv + dk) floats): the portions run in blocks of
+// blk tokens side by side (two passes and a walk over the blocks' states between them; sums in another order than the
+// plain scan's, equal up to float32 rounding).
 FELLM_API int fellm_gated_write_scan(const float* z, int ld, int f_off, int v_off, const float* lower, const float* bias,
                                      float* state, long long slot_stride, const int* item_start, const int* item_slot,
-                                     float* out, int n_items, int H, int dk, int dv, int max_item_rows, cudaStream_t stream) {
+                                     float* out, int n_items, int H, int dk, int dv, int max_item_rows, int blk,
+                                     float* scratch, cudaStream_t stream) {
   if (n_items <= 0) return 0;
   if (dk < 1 || dk > 1024 || dv < 1 || H < 1) return FELLM_ERR_SIZE;
   if (!z || !lower || !bias || !state || !item_start || !item_slot || !out) return FELLM_ERR_ARG;
@@ -705,6 +783,10 @@ FELLM_API int fellm_gated_write_scan(const float* z, int ld, int f_off, int v_of
   a.q = z; a.ld = ld; a.k_off = f_off; a.v_off = v_off; a.state = state; a.slot_stride = slot_stride;
   a.item_start = item_start; a.item_slot = item_slot; a.out = out; a.H = H; a.G = H; a.dk = dk; a.dv = dv;
   a.lower = lower; a.fbias = bias;
+  if (blk > 0 && scratch && max_item_rows > blk) {
+    const size_t n_blocks = (size_t)(max_item_rows + blk - 1) / blk;
+    a.phase = 1; a.blk = blk; a.blk_state = scratch; a.blk_decay = scratch + (size_t)n_items * n_blocks * H * dk * dv;
+  }
   return scan_launch<4, float>(a, n_items, max_item_rows, stream);
 }
 

@@ -608,11 +608,18 @@ def token_shift(x, mu, state, item_start, item_slot, n_items, max_item_rows, out
     return out
 
 
+GATED_WRITE_BLOCK = int(os.environ.get("FELLM_B200_GATED_WRITE_BLOCK", 0))            # tokens of a block (0, the default: the plain scan; measured no faster)
+GATED_WRITE_BLOCK_MIN_ROWS = int(os.environ.get("FELLM_B200_GATED_WRITE_BLOCK_MIN_ROWS", 256))     # shorter portions: the plain scan
+
+
 def gated_write_scan(z, f_off, v_off, lower, bias, state, item_start, item_slot, n_items, H, dk, dv, out=None,
-                     max_item_rows=0):
+                     max_item_rows=0, block=None):
     """Per head S = diag(f) S + (1 - f) v^T, o = S^T q, with q = SiLU(q raw) and f = lower + (1 - lower) sigmoid(f raw +
     bias).  z float32 [T, >= v_off + H*dv]: q raw at column 0 (H x dk), f raw at f_off, v at v_off (H x dv); lower, bias
-    float32 [H*dk]; state float32 [slots, H, dk, dv] (the scan kernel's own layout).  Returns float32 [T, H*dv]."""
+    float32 [H*dk]; state float32 [slots, H, dk, dv] (the scan kernel's own layout).  Returns float32 [T, H*dv].
+    block (default: GATED_WRITE_BLOCK where the step's longest portion has GATED_WRITE_BLOCK_MIN_ROWS rows or more, else 0):
+    the portions run in blocks of that many tokens side by side, every block twice (from zeros, then from the state in
+    front of it), a walk over the blocks' states between the two; equal to the plain scan up to float32 rounding."""
     _dev(z, lower, bias, state, item_start, item_slot)
     T = z.shape[0]
     if dk > MAX_SCAN_KEY_DIM:
@@ -625,10 +632,16 @@ def gated_write_scan(z, f_off, v_off, lower, bias, state, item_start, item_slot,
     if out is None:
         out = torch.empty((T, H * dv), dtype=torch.float32, device=z.device)
     sp, ss = _state_args(state)
+    if block is None:
+        block = GATED_WRITE_BLOCK if max_item_rows >= max(GATED_WRITE_BLOCK_MIN_ROWS, 2) else 0
+    scratch = None
+    if block and max_item_rows > block:
+        scratch = torch.empty(n_items * (-(-max_item_rows // block)) * H * (dk * dv + dk), dtype=torch.float32, device=z.device)
     f = _fn("recurrent", "fellm_gated_write_scan",
-            [_c_p, _c_int, _c_int, _c_int, _c_p, _c_p, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p])
+            [_c_p, _c_int, _c_int, _c_int, _c_p, _c_p, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int,
+             _c_int, _c_p, _c_p])
     _check(f(_p(z), z.stride(0), int(f_off), int(v_off), _p(lower), _p(bias), sp, ss, _p(item_start), _p(item_slot), _p(out),
-             n_items, H, dk, dv, int(max_item_rows), _stream()), "gated_write_scan")
+             n_items, H, dk, dv, int(max_item_rows), int(block or 0), _p(scratch), _stream()), "gated_write_scan")
     return out
 
 
@@ -939,15 +952,15 @@ def moe_gemm(a, w, plan: MoePlan, *, gated: bool, gather: bool, interleaved: boo
     return out
 
 
-def moe_combine(x, y, plan: MoePlan, w):
-    """x float32 [T, d] += sum over a token's choices c, in order, of w[t, c] * y[place of (t, c)]."""
+def moe_combine(x, y, plan: MoePlan, w, store: bool = False):
+    """x float32 [T, d] += sum over a token's choices c, in order, of w[t, c] * y[place of (t, c)] (store: x = the sum)."""
     _dev(x, y, w)
     T, d = x.shape
     assert x.dtype == torch.float32 and y.dtype == torch.float32 and w.dtype == torch.float32
     assert x.is_contiguous() and y.is_contiguous() and w.is_contiguous() and y.shape == (plan.pairs, d)
     residual_written(x)
-    f = _fn("moe", "fellm_moe_combine", [_c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p])
-    _check(f(_p(x), _p(y), _p(plan.place_of), _p(w), T, plan.top, d, _stream()), "moe_combine")
+    f = _fn("moe", "fellm_moe_combine", [_c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_p])
+    _check(f(_p(x), _p(y), _p(plan.place_of), _p(w), T, plan.top, d, int(store), _stream()), "moe_combine")
     return x
 
 

@@ -98,7 +98,9 @@ class RoutedExperts(FeedForward):
         w["down.weight"] = torch.stack([mats[3 * e + 2].to(dt) for e in range(self.E)], 0).contiguous()     # [E, d, ff]
         w["router.weight"] = w["router.weight"].contiguous()
 
-    def forward(self, hn, ctx, out):
+    can_store = True          # forward(store=True) writes its rows instead of adding them
+
+    def forward(self, hn, ctx, out, store=False):
         w = self.w
         idx, score = ops.moe_router(hn, w["router.weight"], self.top, self.renormalize, score=self.score,
                                     correction=w.get("correction"), groups=self.groups, bias=w.get("router.bias"))
@@ -112,11 +114,11 @@ class RoutedExperts(FeedForward):
         if self.plain:
             a = ops.relu2(ops.moe_gemm(hn, first, plan, gated=False, gather=True), hn.dtype)
             y = ops.moe_gemm(a, w["down.weight"], plan, gated=False, gather=False)
-            ops.moe_combine(out, y, plan, score)
+            ops.moe_combine(out, y, plan, score, store=store)
             return out
         a = ops.moe_gemm(hn, w["gate_up.weight"], plan, gated=True, gather=True, interleaved=self.interleaved, act=self.act)
         y = ops.moe_gemm(a, w["down.weight"], plan, gated=False, gather=False)
-        ops.moe_combine(out, y, plan, score)
+        ops.moe_combine(out, y, plan, score, store=store)
         return out
 
     def weight_order(self):

@@ -101,7 +101,8 @@ def test_rescaled_frequencies_of_the_position_part(n, base, scaling):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,G,hd,rot,extra", [(6, 2, 24, 8, 16), (3, 3, 10, 6, 7), (4, 1, 128, 64, 0), (2, 2, 16, 16, 5), (5, 0, 48, 0, 3), (1, 1, 200, 120, 8)])
+@pytest.mark.parametrize("H,G,hd,rot,extra", [(6, 2, 24, 8, 16), (3, 3, 10, 6, 7), (4, 1, 128, 64, 0), (2, 2, 16, 16, 5), (5, 0, 48, 0, 3), (1, 1, 200, 120, 8),
+                                              (4, 1, 128, 64, 5), (6, 2, 64, 32, 2), (3, 1, 32, 16, 5), (2, 1, 256, 0, 5), (5, 3, 64, 64, 7)])
 def test_rotation_then_unit_norm_in_place(dtype, H, G, hd, rot, extra):
     """Heads whose rotated part is a thousand times their unrotated part (and the other way round): a norm over the wrong
     elements, or taken in front of a rotation that did not keep the length, would show; positions up to 100,000 (the angle
@@ -131,11 +132,13 @@ def test_rotation_then_unit_norm_in_place(dtype, H, G, hd, rot, extra):
     assert torch.equal(y[:, (H + G) * hd:], x.to(DEV)[:, (H + G) * hd:])           # values and what lies behind them are not touched
 
 
+@pytest.mark.parametrize("block", [0, 16, 64])
 @pytest.mark.parametrize("H,dk,dv", [(3, 20, 12), (1, 64, 8), (9, 3, 5), (2, 128, 64), (4, 48, 32), (2, 5, 33)])
-def test_gated_write_recurrence_over_portions_and_slots(H, dk, dv):
+def test_gated_write_recurrence_over_portions_and_slots(H, dk, dv, block):
     """The scan in portions of 1, 2, 17, ... tokens of two requests in interleaved slots against the token-by-token
     recurrence; the gate's logits reach both bounds (f = lower and f = 1) and a state written at the first token is read
-    three hundred tokens later through gates close to one."""
+    three hundred tokens later through gates close to one.  block > 0: portions longer than a block run in blocks side by
+    side (beside a request's single token in the same step), which must give the same outputs and leave the same state."""
     from fellm_b200 import ops
     g = torch.Generator().manual_seed(dk * dv)
     n, m = H * dk, H * dv
@@ -162,7 +165,7 @@ def test_gated_write_recurrence_over_portions_and_slots(H, dk, dv):
                 sl.append(s)
         z = torch.cat(rows).to(DEV)
         o = ops.gated_write_scan(z, n, 2 * n, lower.to(DEV), bias.to(DEV), state, _i32(starts), _i32(sl), len(sl), H, dk, dv,
-                                 max_item_rows=max(starts[i + 1] - starts[i] for i in range(len(sl))))
+                                 max_item_rows=max(starts[i + 1] - starts[i] for i in range(len(sl))), block=block)
         for i, s in enumerate(sl):
             got[s].append(o[starts[i]:starts[i + 1]].cpu())
             at[s] += starts[i + 1] - starts[i]
