@@ -236,6 +236,9 @@ FELLM_API int fellm_lowrank_expand(const float* z, int ldz, const void* W2, int 
 //   decay and bonus:  B = r,  G = w,  K = k,  c = sum_i r_i u_i k_i,  A unused
 //   gated write (q = SiLU(q raw), f = l + (1 - l) sigmoid(f raw + bias), l a lower bound per channel):
 //       B = f q,  G = f,  K = 1 - f,  c = sum_i (1 - f_i) q_i      (S^T q after the write = S^T (f q) + v c)
+//   the same, prepared (mode 5): a kernel in front has left f q and f where q raw and f raw stood and c beside them, once a
+//   token and head; the producers then only copy (every column tile of a head repeats the staging, and with the gate's
+//   exponentials in it the staging was two thirds of the kernel's instructions)
 // so the chain from token to token is one reduction and one multiply-add per element.  Eight producer warps stage
 // these vectors for the next tokens (loads, unit norms, decays, sigmoids) in shared memory while four consumer
 // warps run the chain over the tokens staged before: one block barrier per stage.  KS is chosen from the model's
@@ -320,6 +323,7 @@ __device__ __forceinline__ void scan_stage(const ScanArgs& a, float* buf, int DK
     logit_b = a.small[row * a.lds + a.b_off + h];
     if (MODE == 0) logit_a = a.small[row * a.lds + a.a_off + h];
   }
+  if (MODE == 5 && ptid < n_tok) { logit_b = 1.f; logit_a = a.small[(size_t)(row0 + ptid) * a.lds + h]; }      // beta, c
   if (a.vec) {
     // eight (bfloat16) or four (float32) elements a load: 16 bytes of q, of k and, where there is one, of the decay
     constexpr int VE = sizeof(TA) == 2 ? 8 : 4;
@@ -375,7 +379,7 @@ __device__ __forceinline__ void scan_stage(const ScanArgs& a, float* buf, int DK
     const int idx = ptid + u * PT;
     if (idx < n_tok * COLS) V[idx] = vreg[u];
   }
-  if (MODE < 2 && ptid < n_tok) { beta[ptid] = logit_b; cc[ptid] = logit_a; }
+  if ((MODE < 2 || MODE == 5) && ptid < n_tok) { beta[ptid] = logit_b; cc[ptid] = logit_a; }
   producers_sync();
   // a warp takes TPW tokens at once: their sums and butterflies are independent chains
   constexpr int TPW = SC_MAX_TOK / SC_PRODUCERS;
@@ -400,6 +404,18 @@ __device__ __forceinline__ void scan_stage(const ScanArgs& a, float* buf, int DK
     for (int u = 0; u < TPW; ++u) {
       const int t = pw + u * SC_PRODUCERS;
       if (t < n_tok && lane == 0) { cc[t] = c[u]; beta[t] = 1.f; }
+    }
+  } else if (MODE == 5) {
+    // gated write, prepared: B = f q is staged as it is, KK holds f: G = f, K = 1 - f (rows behind dk: zeros)
+#pragma unroll
+    for (int u = 0; u < TPW; ++u) {
+      const int t = pw + u * SC_PRODUCERS;
+      if (t >= n_tok) continue;
+      float* Gt = Gd + t * DKP; float* Kt = KK + t * DKP;
+      for (int i = lane; i < DKP; i += 32) {
+        const float f = Kt[i];
+        Gt[i] = f; Kt[i] = i < dk ? 1.0f - f : 0.f;
+      }
     }
   } else if (MODE == 4) {
     // gated write: everything of the gate in float32; rows behind dk keep K = 0, so the state's padding stays zero
@@ -505,7 +521,7 @@ __global__ void __launch_bounds__(SC_THREADS) scan_kernel(ScanArgs a) {
   const int j = col0 + cw;
   const bool live = consumer && j < a.dv;
   float* Sg = a.state + (size_t)a.item_slot[item] * a.slot_stride + (size_t)h * a.dk * a.dv;
-  constexpr bool BLOCKS = MODE == 4;                       // (the modes that run portions in blocks)
+  constexpr bool BLOCKS = MODE == 4 || MODE == 5;                       // (the modes that run portions in blocks)
   const int phase = BLOCKS ? a.phase : 0;
   float* Dg = nullptr;
   if (BLOCKS && phase) {
@@ -573,9 +589,52 @@ __global__ void __launch_bounds__(SC_THREADS) scan_kernel(ScanArgs a) {
         }
         nv = V[t * COLS + cw]; nbeta = beta[t]; ncc = cc[t];
       };
-      if (AHEAD) fetch(0);
+      // Recurrences whose write does not read the state (u = v): four tokens a round.  The state's chain from token to
+      // token is one multiply-add an element; what takes long is the butterfly that sums a column's lanes, and the four
+      // tokens' butterflies are independent: they go round together.  Same operations, same order, same numbers as the
+      // token-by-token loop below.
+      constexpr bool ROUNDS = MODE >= 2;
+      if (ROUNDS) {
+        constexpr int TB = 4;
+        for (int t = 0; t < n_tok; t += TB) {
+          float d2[TB], vv[TB], ctt[TB];
+#pragma unroll
+          for (int b = 0; b < TB; ++b) {
+            d2[b] = 0.f; vv[b] = 0.f; ctt[b] = 0.f;
+            if (t + b < n_tok) {
+              const int tt = t + b;
+              const float v = V[tt * COLS + cw];
+              float p2[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+              for (int r4 = 0; r4 < R4; ++r4) {
+                const int at = tt * dq + ks + KS * r4;
+                const float4 cB = B4[at], cG = G4[at], cK = K4[at];
+                p2[0] = fmaf(S[4 * r4], cB.x, p2[0]); p2[1] = fmaf(S[4 * r4 + 1], cB.y, p2[1]);
+                p2[2] = fmaf(S[4 * r4 + 2], cB.z, p2[2]); p2[3] = fmaf(S[4 * r4 + 3], cB.w, p2[3]);
+                S[4 * r4] = fmaf(cK.x, v, cG.x * S[4 * r4]);
+                S[4 * r4 + 1] = fmaf(cK.y, v, cG.y * S[4 * r4 + 1]);
+                S[4 * r4 + 2] = fmaf(cK.z, v, cG.z * S[4 * r4 + 2]);
+                S[4 * r4 + 3] = fmaf(cK.w, v, cG.w * S[4 * r4 + 3]);
+                if (BLOCKS && phase == 1) {
+                  Dp[4 * r4] *= cG.x; Dp[4 * r4 + 1] *= cG.y; Dp[4 * r4 + 2] *= cG.z; Dp[4 * r4 + 3] *= cG.w;
+                }
+              }
+              d2[b] = (p2[0] + p2[1]) + (p2[2] + p2[3]); vv[b] = v; ctt[b] = cc[tt];
+            }
+          }
+          for (int o = 1; o < KS; o <<= 1) {
+#pragma unroll
+            for (int b = 0; b < TB; ++b) d2[b] += __shfl_xor_sync(0xffffffffu, d2[b], o);
+          }
+#pragma unroll
+          for (int b = 0; b < TB; ++b)
+            if (t + b < n_tok && ks == 0 && live && phase != 1)
+              a.out[(size_t)(row_begin + t0 + t + b) * ((size_t)a.H * a.dv) + (size_t)h * a.dv + j] = fmaf(vv[b], ctt[b], d2[b]);
+        }
+      }
+      if (AHEAD && !ROUNDS) fetch(0);
 #pragma unroll 2
-      for (int t = 0; t < n_tok; ++t) {
+      for (int t = 0; t < (ROUNDS ? 0 : n_tok); ++t) {
         if (!AHEAD) fetch(t);
         float4 cA[R4], cB[R4], cG[R4], cK[R4];
 #pragma unroll
@@ -766,16 +825,43 @@ FELLM_API int fellm_retention_scan(const void* qkv, int is_bf16, int ld, int k_o
   return is_bf16 ? scan_launch<3, bf16>(a, n_items, max_item_rows, stream) : scan_launch<3, float>(a, n_items, max_item_rows, stream);
 }
 
+// In front of the prepared form: a warp a (token, head) turns q raw into f q and f raw into f where they stand and leaves
+// c = sum_i (1 - f_i) q_i in cc [T, H]: the same operations in the same order as the unprepared stage's, so both forms
+// hand the consumers the same numbers.
+__global__ void __launch_bounds__(128)
+gated_write_prep_kernel(float* __restrict__ z, int ld, int f_off, const float* __restrict__ lower, const float* __restrict__ fbias,
+                        float* __restrict__ cc, int T, int H, int dk) {
+  const int warp = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (warp >= T * H) return;
+  const int t = warp / H, h = warp - t * H;
+  float* qr = z + (size_t)t * ld + (size_t)h * dk;
+  float* fr = qr + f_off;
+  const float* lo = lower + (size_t)h * dk; const float* fb = fbias + (size_t)h * dk;
+  float c = 0.f;
+  for (int i = lane; i < dk; i += 32) {
+    const float q = silu_f(qr[i]), l = lo[i];
+    const float f = fmaf(1.0f - l, sigmoid_f(fr[i] + fb[i]), l);
+    const float w = 1.0f - f;
+    c = fmaf(w, q, c);
+    qr[i] = f * q; fr[i] = f;
+  }
+  c = warp_sum(c);
+  if (lane == 0) cc[(size_t)t * H + h] = c;
+}
+
 // Gated write: S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T, o_t = S_t^T q_t with q = SiLU(q raw) and
 // f = lower + (1 - lower) sigmoid(f raw + bias).  z float32 [T, ld]: q raw at column 0 (H x dk), f raw at f_off (H x dk),
 // v at v_off (H x dv), as their product left them; lower, bias float32 [H * dk].
 // blk > 0 (with scratch of n_items * ceil(max_item_rows / blk) * H * (dk * dv + dk) floats): the portions run in blocks of
 // blk tokens side by side (two passes and a walk over the blocks' states between them; sums in another order than the
 // plain scan's, equal up to float32 rounding).
-FELLM_API int fellm_gated_write_scan(const float* z, int ld, int f_off, int v_off, const float* lower, const float* bias,
+// prep (float32 [T, H], with T the rows of z): the gates are computed once a token and head by a kernel in front, IN PLACE
+// (z's q and f columns then hold f q and f), and the scan's producers only copy: for portions; a decode step's single
+// tokens keep the one launch.
+FELLM_API int fellm_gated_write_scan(float* z, int ld, int f_off, int v_off, const float* lower, const float* bias,
                                      float* state, long long slot_stride, const int* item_start, const int* item_slot,
                                      float* out, int n_items, int H, int dk, int dv, int max_item_rows, int blk,
-                                     float* scratch, cudaStream_t stream) {
+                                     float* scratch, float* prep, int T, cudaStream_t stream) {
   if (n_items <= 0) return 0;
   if (dk < 1 || dk > 1024 || dv < 1 || H < 1) return FELLM_ERR_SIZE;
   if (!z || !lower || !bias || !state || !item_start || !item_slot || !out) return FELLM_ERR_ARG;
@@ -786,6 +872,11 @@ FELLM_API int fellm_gated_write_scan(const float* z, int ld, int f_off, int v_of
   if (blk > 0 && scratch && max_item_rows > blk) {
     const size_t n_blocks = (size_t)(max_item_rows + blk - 1) / blk;
     a.phase = 1; a.blk = blk; a.blk_state = scratch; a.blk_decay = scratch + (size_t)n_items * n_blocks * H * dk * dv;
+  }
+  if (prep && T > 0) {
+    gated_write_prep_kernel<<<(unsigned)(((long long)T * H + 3) / 4), 128, 0, stream>>>(z, ld, f_off, lower, bias, prep, T, H, dk);
+    a.small = prep; a.lds = H;
+    return scan_launch<5, float>(a, n_items, max_item_rows, stream);
   }
   return scan_launch<4, float>(a, n_items, max_item_rows, stream);
 }

@@ -610,16 +610,20 @@ def token_shift(x, mu, state, item_start, item_slot, n_items, max_item_rows, out
 
 GATED_WRITE_BLOCK = int(os.environ.get("FELLM_B200_GATED_WRITE_BLOCK", 0))            # tokens of a block (0, the default: the plain scan; measured no faster)
 GATED_WRITE_BLOCK_MIN_ROWS = int(os.environ.get("FELLM_B200_GATED_WRITE_BLOCK_MIN_ROWS", 256))     # shorter portions: the plain scan
+GATED_WRITE_PREP_MIN_ROWS = int(os.environ.get("FELLM_B200_GATED_WRITE_PREP_MIN_ROWS", 16))       # a step's longest portion from which the gates are prepared in front
 
 
 def gated_write_scan(z, f_off, v_off, lower, bias, state, item_start, item_slot, n_items, H, dk, dv, out=None,
-                     max_item_rows=0, block=None):
+                     max_item_rows=0, block=None, prepared=None):
     """Per head S = diag(f) S + (1 - f) v^T, o = S^T q, with q = SiLU(q raw) and f = lower + (1 - lower) sigmoid(f raw +
     bias).  z float32 [T, >= v_off + H*dv]: q raw at column 0 (H x dk), f raw at f_off, v at v_off (H x dv); lower, bias
     float32 [H*dk]; state float32 [slots, H, dk, dv] (the scan kernel's own layout).  Returns float32 [T, H*dv].
     block (default: GATED_WRITE_BLOCK where the step's longest portion has GATED_WRITE_BLOCK_MIN_ROWS rows or more, else 0):
     the portions run in blocks of that many tokens side by side, every block twice (from zeros, then from the state in
-    front of it), a walk over the blocks' states between the two; equal to the plain scan up to float32 rounding."""
+    front of it), a walk over the blocks' states between the two; equal to the plain scan up to float32 rounding.
+    prepared (default: where the longest portion has GATED_WRITE_PREP_MIN_ROWS rows or more): a kernel in front computes the
+    gates once a token and head IN PLACE (z's q and f columns then hold f q and f) and the scan's producers only copy;
+    the same numbers as the one-launch form, which single tokens keep."""
     _dev(z, lower, bias, state, item_start, item_slot)
     T = z.shape[0]
     if dk > MAX_SCAN_KEY_DIM:
@@ -637,11 +641,14 @@ def gated_write_scan(z, f_off, v_off, lower, bias, state, item_start, item_slot,
     scratch = None
     if block and max_item_rows > block:
         scratch = torch.empty(n_items * (-(-max_item_rows // block)) * H * (dk * dv + dk), dtype=torch.float32, device=z.device)
+    if prepared is None:
+        prepared = max_item_rows >= GATED_WRITE_PREP_MIN_ROWS
+    prep = torch.empty((T, H), dtype=torch.float32, device=z.device) if prepared else None
     f = _fn("recurrent", "fellm_gated_write_scan",
             [_c_p, _c_int, _c_int, _c_int, _c_p, _c_p, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int,
-             _c_int, _c_p, _c_p])
+             _c_int, _c_p, _c_p, _c_int, _c_p])
     _check(f(_p(z), z.stride(0), int(f_off), int(v_off), _p(lower), _p(bias), sp, ss, _p(item_start), _p(item_slot), _p(out),
-             n_items, H, dk, dv, int(max_item_rows), int(block or 0), _p(scratch), _stream()), "gated_write_scan")
+             n_items, H, dk, dv, int(max_item_rows), int(block or 0), _p(scratch), _p(prep), T, _stream()), "gated_write_scan")
     return out
 
 

@@ -255,8 +255,8 @@ class Attention(Mixer):
         return out
 
     def _on_tensor_cores(self, qkv) -> bool:
-        return (qkv.dtype == torch.bfloat16 and self.vd == self.hd and self.hd % 16 == 0 and self.H // self.G <= 64
-                and ops.GENERAL_ATTENTION_MMA)
+        return (qkv.dtype == torch.bfloat16 and self.vd == self.hd and self.hd % 16 == 0 and self.hd <= 256
+                and self.H // self.G <= 64 and ops.GENERAL_ATTENTION_MMA)
 
     def weight_order(self):
         return [self.w["qkv.weight"], self.w["out_proj.weight"]]

@@ -132,13 +132,14 @@ def test_rotation_then_unit_norm_in_place(dtype, H, G, hd, rot, extra):
     assert torch.equal(y[:, (H + G) * hd:], x.to(DEV)[:, (H + G) * hd:])           # values and what lies behind them are not touched
 
 
-@pytest.mark.parametrize("block", [0, 16, 64])
+@pytest.mark.parametrize("block,prepared", [(0, False), (0, True), (16, True), (64, False), (0, None)])
 @pytest.mark.parametrize("H,dk,dv", [(3, 20, 12), (1, 64, 8), (9, 3, 5), (2, 128, 64), (4, 48, 32), (2, 5, 33)])
-def test_gated_write_recurrence_over_portions_and_slots(H, dk, dv, block):
+def test_gated_write_recurrence_over_portions_and_slots(H, dk, dv, block, prepared):
     """The scan in portions of 1, 2, 17, ... tokens of two requests in interleaved slots against the token-by-token
     recurrence; the gate's logits reach both bounds (f = lower and f = 1) and a state written at the first token is read
     three hundred tokens later through gates close to one.  block > 0: portions longer than a block run in blocks side by
-    side (beside a request's single token in the same step), which must give the same outputs and leave the same state."""
+    side (beside a request's single token in the same step), which must give the same outputs and leave the same state.
+    prepared: the gates are computed by a kernel in front, in place (None: the choice by the step's longest portion)."""
     from fellm_b200 import ops
     g = torch.Generator().manual_seed(dk * dv)
     n, m = H * dk, H * dv
@@ -163,9 +164,10 @@ def test_gated_write_recurrence_over_portions_and_slots(H, dk, dv, block):
                 rows.append(seqs[s][at[s]:at[s] + k])
                 starts.append(starts[-1] + k)
                 sl.append(s)
-        z = torch.cat(rows).to(DEV)
+        z = torch.cat(rows).to(DEV)             # (a copy: the prepared form writes into it)
         o = ops.gated_write_scan(z, n, 2 * n, lower.to(DEV), bias.to(DEV), state, _i32(starts), _i32(sl), len(sl), H, dk, dv,
-                                 max_item_rows=max(starts[i + 1] - starts[i] for i in range(len(sl))), block=block)
+                                 max_item_rows=max(starts[i + 1] - starts[i] for i in range(len(sl))), block=block,
+                                 prepared=prepared)
         for i, s in enumerate(sl):
             got[s].append(o[starts[i]:starts[i + 1]].cpu())
             at[s] += starts[i + 1] - starts[i]
