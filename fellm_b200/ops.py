@@ -591,10 +591,14 @@ def token_shift_mix(h, mu, state, item_start, item_slot, n_items, max_item_rows,
     return out
 
 
-def token_shift(x, mu, state, item_start, item_slot, n_items, max_item_rows, out_dtype, out=None):
+def token_shift(x, mu, state, item_start, item_slot, n_items, max_item_rows, out_dtype, out=None, row_item=None):
     """x float32 [T, d] -> x + (x_prev - x) * mu in out_dtype, x_prev the row before (the slot's float32 state [slots, d]
-    before a portion's first row; the state then takes the portion's last row of x as it is)."""
-    _dev(x, mu, state, item_start, item_slot)
+    before a portion's first row; the state then takes the portion's last row of x as it is).  row_item int32 [T] (each
+    row's item): lets widths of a multiple of 4 run with 16-byte loads, a thread four channels of a row."""
+    _dev(x, mu, state, item_start, item_slot, row_item)
+    if row_item is not None:
+        _i32(row_item, "row_item")
+        assert row_item.numel() >= x.shape[0]
     T, d = x.shape
     assert x.dtype == torch.float32 and x.is_contiguous() and mu.dtype == torch.float32 and mu.numel() == d and mu.is_contiguous()
     assert state.shape[1:] == (d,)
@@ -602,9 +606,9 @@ def token_shift(x, mu, state, item_start, item_slot, n_items, max_item_rows, out
     if out is None:
         out = torch.empty((T, d), dtype=out_dtype, device=x.device)
     sp, ss = _state_args(state)
-    f = _fn("recurrent", "fellm_token_shift", [_c_p, _c_p, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p])
-    _check(f(_p(x), _p(mu), sp, ss, _p(item_start), _p(item_slot), _p(out), _is_bf16(out), T, n_items, d, int(max_item_rows),
-             _stream()), "token_shift")
+    f = _fn("recurrent", "fellm_token_shift", [_c_p, _c_p, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p])
+    _check(f(_p(x), _p(mu), sp, ss, _p(item_start), _p(item_slot), _p(row_item), _p(out), _is_bf16(out), T, n_items, d,
+             int(max_item_rows), _stream()), "token_shift")
     return out
 
 

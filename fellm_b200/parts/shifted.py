@@ -58,7 +58,7 @@ class TokenShifted(Mixer):
         else:
             mine, rest = cache[0], list(cache[1:])
         h = ops.token_shift(x, self.w["shift"], mine.states, ctx.item_start, mine.item_slot, ctx.n_items,
-                            ctx.max_item_rows, self.act_dtype)
+                            ctx.max_item_rows, self.act_dtype, row_item=ctx.row_item)
         inner_cache = rest if self._inner_is_list else (rest[0] if rest else None)
         return self.inner.forward(h, ctx, inner_cache, out, reads_only=reads_only, **kw)
 

@@ -55,10 +55,12 @@ def test_layer_norm_and_its_sum_into_the_stream(T, d):
     assert torch.equal(cast, xs.bfloat16())
 
 
+@pytest.mark.parametrize("d,with_items", [(40, False), (40, True), (128, True), (42, True)])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
-def test_token_shift_reads_the_row_before_from_the_batch_or_from_the_slot(out_dtype):
+def test_token_shift_reads_the_row_before_from_the_batch_or_from_the_slot(out_dtype, d, with_items):
+    """with_items: the rows' items are handed over, which lets widths of a multiple of 4 take 16-byte loads."""
     from fellm_b200 import ops
-    d, slots = 40, 4
+    slots = 4
     g = torch.Generator().manual_seed(1)
     mu = torch.rand(d, generator=g)
     mu[0], mu[1] = 0.0, 1.0
@@ -73,7 +75,8 @@ def test_token_shift_reads_the_row_before_from_the_batch_or_from_the_slot(out_dt
             starts.append(starts[-1] + n)
             sl.append(s)
         x = torch.cat(rows).to(DEV)
-        out = ops.token_shift(x, mu.to(DEV), state, _i32(starts), _i32(sl), 2, max(sizes), out_dtype)
+        row_item = _i32([k for k in range(2) for _ in range(sizes[k])]) if with_items else None
+        out = ops.token_shift(x, mu.to(DEV), state, _i32(starts), _i32(sl), 2, max(sizes), out_dtype, row_item=row_item)
         for k, (s, n) in enumerate(zip((2, 0), sizes)):
             got[s].append(out[starts[k]:starts[k + 1]].float().cpu())
             at[s] += n
