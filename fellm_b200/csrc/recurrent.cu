@@ -292,7 +292,7 @@ FELLM_API int fellm_lowrank_expand(const float* z, int ldz, const void* W2, int 
 #define SC_CONSUMERS 4
 #define SC_PRODUCERS 8
 #define SC_THREADS ((SC_CONSUMERS + SC_PRODUCERS) * 32)
-#define SC_MAX_TOK 16
+#define SC_MAX_TOK 32
 
 struct ScanArgs {
   // delta rule: q at qkv, k at qkv + k_off, v at qkv + v_off of a row (ld elements); decay and bonus: r, k, v rows
@@ -372,27 +372,41 @@ __device__ __forceinline__ void scan_stage(const ScanArgs& a, float* buf, int DK
   if (a.vec) {
     // eight (bfloat16) or four (float32) elements a load: 16 bytes of q, of k and, where there is one, of the decay
     constexpr int VE = sizeof(TA) == 2 ? 8 : 4;
+    constexpr int UV = sizeof(TA) == 2 ? 2 : 4;          // vectors a thread keeps in flight: a stage's loads are ONE round trip to memory
     const int per_tok = DKP / VE, nvec = n_tok * per_tok;
-    for (int idx = ptid; idx < nvec; idx += PT) {
-      const int t = idx / per_tok, i = (idx - t * per_tok) * VE;
-      float x0[VE], x1[VE], x2[VE];
+    for (int base = ptid; base < nvec; base += PT * UV) {
+      float x0[UV][VE], x1[UV][VE], x2[UV][VE];
 #pragma unroll
-      for (int e = 0; e < VE; ++e) x0[e] = x1[e] = x2[e] = 0.f;
-      if (i < dk) {
-        const size_t row = (size_t)(row0 + t);
-        load_vec<VE>(x0p + row * a.ld + i, x0);
-        load_vec<VE>(x1p + row * a.ld + i, x1);
-        if (MODE == 1 || MODE == 2) {
+      for (int u = 0; u < UV; ++u) {
 #pragma unroll
-          for (int e = 0; e < VE; e += 4) *(float4*)(x2 + e) = *(const float4*)(x2p + row * ((size_t)a.H * dk) + i + e);
+        for (int e = 0; e < VE; ++e) x0[u][e] = x1[u][e] = x2[u][e] = 0.f;
+        const int idx = base + u * PT;
+        if (idx < nvec) {
+          const int t = idx / per_tok, i = (idx - t * per_tok) * VE;
+          if (i < dk) {
+            const size_t row = (size_t)(row0 + t);
+            load_vec<VE>(x0p + row * a.ld + i, x0[u]);
+            load_vec<VE>(x1p + row * a.ld + i, x1[u]);
+            if (MODE == 1 || MODE == 2) {
+#pragma unroll
+              for (int e = 0; e < VE; e += 4) *(float4*)(x2[u] + e) = *(const float4*)(x2p + row * ((size_t)a.H * dk) + i + e);
+            }
+          }
         }
       }
-      const int o = t * DKP + i;
 #pragma unroll
-      for (int e = 0; e < VE; e += 4) {
-        *(float4*)(B + o + e) = *(float4*)(x0 + e);
-        *(float4*)(KK + o + e) = *(float4*)(x1 + e);
-        *(float4*)(Gd + o + e) = *(float4*)(x2 + e);
+      for (int u = 0; u < UV; ++u) {
+        const int idx = base + u * PT;
+        if (idx < nvec) {
+          const int t = idx / per_tok, i = (idx - t * per_tok) * VE;
+          const int o = t * DKP + i;
+#pragma unroll
+          for (int e = 0; e < VE; e += 4) {
+            *(float4*)(B + o + e) = *(float4*)(x0[u] + e);
+            *(float4*)(KK + o + e) = *(float4*)(x1[u] + e);
+            *(float4*)(Gd + o + e) = *(float4*)(x2[u] + e);
+          }
+        }
       }
     }
   } else {
@@ -791,7 +805,7 @@ static int scan_launch(ScanArgs& a, int n_items, int max_item_rows, cudaStream_t
   }
   const int CPW = 32 / KS, COLS = SC_CONSUMERS * CPW, DKP = 4 * KS * R4;
   const int per_tok = (4 * DKP + COLS + 4) * (int)sizeof(float);
-  int tc = 40960 / per_tok;
+  int tc = 81920 / per_tok;          // (two buffers: up to 160 KB a CTA; a stage is as long as the producers' round trip to memory is worth)
   a.tc = tc < 1 ? 1 : (tc > SC_MAX_TOK ? SC_MAX_TOK : tc);
   if (max_item_rows > 0 && max_item_rows < a.tc) a.tc = max_item_rows;      // a decode step stages one token: 4 KB a block, not 67
   if (a.phase && a.tc > 8) a.tc = 8;                                        // blocks side by side: less shared memory, more CTAs an SM
