@@ -103,7 +103,14 @@ CFG_W = config(256, 1024, [
     layer(attention(16, 4, 64, 64, 4096, 0.125, rot=32, scaling=(8.0, 1.0, 4.0, 128), kv_from=1), moe(256, 16, 4)),
 ], side=16)
 
-CONFIGS = {"A": (CFG_A, 41), "B": (CFG_B, 42), "C": (CFG_C, 43), "M": (CFG_M, 44), "W": (CFG_W, 45)}
+# O: a width and a vocabulary that are odd (no 8- or 16-byte row anywhere: every kernel's scalar form), odd head sizes
+CFG_O = config(97, 37, [
+    layer(attention(3, 1, 7, 5, 9, 0.4, rot=6, base=50.0, scaling=(2.0, 0.5, 2.0, 16)), moe(11, 5, 2)),
+    layer(hgrn2(2, 9, 3), dense(21)),
+    layer(attention(2, 1, 7, 5, 30, 0.4, rot=6, base=50.0, scaling=(2.0, 0.5, 2.0, 16), kv_from=0), dense(13)),
+], emb=3.0, side=3)
+
+CONFIGS = {"A": (CFG_A, 41), "B": (CFG_B, 42), "C": (CFG_C, 43), "M": (CFG_M, 44), "W": (CFG_W, 45), "O": (CFG_O, 46)}
 PAGE_TOKENS = {"M": 64, "W": 64}          # (the other small configurations run with pages of 16)
 _tmp = tempfile.TemporaryDirectory(prefix="fellm_b200_nalizen_")
 

@@ -256,7 +256,7 @@ def engines(request):
     made.clear()
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C", "M"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "M", "O"])
 def test_whole_prompt(engines, name):
     T = 150
     got = U.run_cuts(engines(name), "a", U.tokens(name, T, 0), [T])
@@ -302,7 +302,8 @@ def test_prompt_against_token_by_token(engines, name):
 
 
 @pytest.mark.parametrize("name,cuts", [("A", [2, 2, 3, 17, 2, 21, 1, 1, 23, 2, 48]), ("B", [7, 2, 71, 2, 9, 64, 3]),
-                                       ("C", [15, 2, 1, 16, 17, 2, 33]), ("M", [31, 2, 30, 1, 2, 63, 2, 7]), ("M", [64, 2, 69])])
+                                       ("C", [15, 2, 1, 16, 17, 2, 33]), ("M", [31, 2, 30, 1, 2, 63, 2, 7]), ("M", [64, 2, 69]),
+                                       ("O", [2, 9, 1, 8, 2, 31, 16])])
 def test_portions_of_many_sizes(engines, name, cuts):
     T = 170
     eng = engines(name)
